@@ -73,6 +73,11 @@ def _ensure_builtin() -> None:
 
     if SETENEX not in ARCHITECTURES:
         register_architecture(SETENEX, SetenexConfig.from_dict, setenex_spec, needs_tensor_shapes=True)
+    from ..models.gukirax import gukirax_spec
+    from .gukirax_config import ARCHITECTURE as GUKIRAX, GukiraxConfig
+
+    if GUKIRAX not in ARCHITECTURES:
+        register_architecture(GUKIRAX, GukiraxConfig.from_dict, gukirax_spec)
 
 
 _LLAMA3_32 = RopeScaling(factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)
@@ -117,3 +122,7 @@ PRESETS.update(MOPILORN_PRESETS)
 from .setenex_config import SETENEX_PRESETS  # noqa: E402
 
 PRESETS.update(SETENEX_PRESETS)
+
+from .gukirax_config import GUKIRAX_PRESETS  # noqa: E402
+
+PRESETS.update(GUKIRAX_PRESETS)

@@ -657,3 +657,24 @@ KVF_API int kvf_set_pdl(int enabled) {
 
 KVF_ELEMENTWISE_API(f32, float)
 KVF_ELEMENTWISE_API(bf16, bf16)
+
+// logits <- cap * tanh(scale * logits / cap) in place (cap == 0: scale * logits): an output head whose logits are
+// scaled and then capped softly.
+namespace {
+__global__ void __launch_bounds__(256) scale_softcap_kernel(float* __restrict__ x, long long n, float scale, float cap) {
+  pdl_launch();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = x[i] * scale;
+    x[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  }
+}
+
+}  // namespace
+
+KVF_API int kvf_scale_softcap_f32(float* x, long long n, float scale, float cap, cudaStream_t st) {
+  if (n <= 0) return 0;
+  long long g = (n + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  return launch(scale_softcap_kernel, dim3((unsigned)g), dim3(256), 0, st, x, n, scale, cap);
+}

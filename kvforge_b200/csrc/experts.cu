@@ -50,7 +50,7 @@ template <typename T, int RT>
 __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x, long long x_stride,
                                                          const float* __restrict__ router, const float* __restrict__ correction,
                                                          int n_tokens, int W, int E, int top, int groups, int keep,
-                                                         float norm_eps, int vec, int* __restrict__ ids, float* __restrict__ wts) {
+                                                         float norm_eps, int vec, int flags, int* __restrict__ ids, float* __restrict__ wts) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float sm[];
@@ -87,7 +87,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
     for (int t = 0; t < RT; ++t) {
       const float zt = warp_sum(z[t]);
       if (lane == 0) {
-        const float s = 1.f / (1.f + expf(-zt));
+        // flags bit 0: the scores are a softmax over all experts, made below from the logits kept here
+        const float s = (flags & 1) ? zt : 1.f / (1.f + expf(-zt));
         sm[t * per_token + e] = s;
         sm[t * per_token + E + e] = s + (correction ? correction[e] : 0.f);
       }
@@ -100,6 +101,22 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
   float* ch = sc + E;
   float* gs = ch + E;
   float* ga = gs + groups;
+  if (flags & 1) {
+    // softmax over the experts: a lane adds its experts in order, then the lanes are summed in a fixed tree
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(sc[e] - mx);
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) {
+      const float s = expf(sc[e] - mx) / sum;
+      sc[e] = s;
+      ch[e] = s + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+  }
   if (groups > 1 && keep < groups) {
     // a group is ranked by the sum of the top two shifted scores among its members; the `keep` best-ranked stay
     const int per = E / groups;
@@ -159,6 +176,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
     }
     __syncwarp();
   }
+  if (flags & 2) return;  // the weights are the chosen scores as they are
   const float inv = 1.f / (total + norm_eps);
   for (int k = lane; k < top; k += 32) my_w[k] *= inv;
 }
@@ -206,15 +224,23 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
 }
 
 __device__ __forceinline__ float gelu_erf(float z) { return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f)); }
+// an expert's activation: 0 the exact GELU, 1 the square of relu
+__device__ __forceinline__ float expert_act(float z, int kind) {
+  if (kind == 1) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  return gelu_erf(z);
+}
 
 // A tile of TM rows of one expert times a tile of 64 of its output columns, on the FP32 pipes.
-//   UP:   A row i = x[order[i] / top], B = w[e] [n_out][K], out act[i][col] = T(gelu(acc))
+//   UP:   A row i = x[order[i] / top], B = w[e] [n_out][K], out act[i][col] = T(act(acc))
 //   else: A row i = act[i],            B = w[e] [n_out][K], out y[order[i]][col] = acc (float)
 template <typename T, bool UP>
 __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ a, long long a_stride, const T* __restrict__ w,
                                                            const int* __restrict__ order, const int* __restrict__ tiles,
                                                            const int* __restrict__ meta, int top, int K, int n_out,
-                                                           T* __restrict__ act, float* __restrict__ y) {
+                                                           T* __restrict__ act, float* __restrict__ y, int act_kind) {
   pdl_launch();
   pdl_wait();
   constexpr int BN = 64, BK = 16;
@@ -269,7 +295,7 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
       const int c = col0 + tx * 4 + j;
       if (c >= n_out) continue;
       if (UP)
-        act[(size_t)(row0 + r) * n_out + c] = from_float<T>(gelu_erf(acc[i][j]));
+        act[(size_t)(row0 + r) * n_out + c] = from_float<T>(expert_act(acc[i][j], act_kind));
       else
         y[(size_t)order[row0 + r] * n_out + c] = acc[i][j];
     }
@@ -305,7 +331,7 @@ template <int NT, int STAGES, bool UP>
 __global__ void __launch_bounds__(128) moe_product_mma_kernel(const bf16* __restrict__ a, long long a_stride, const bf16* __restrict__ w,
                                                                const int* __restrict__ order, const int* __restrict__ tiles,
                                                                const int* __restrict__ meta, int top, int K, int n_out,
-                                                               bf16* __restrict__ act, float* __restrict__ y) {
+                                                               bf16* __restrict__ act, float* __restrict__ y, int act_kind) {
   constexpr int BN = 64, BK = 64, THREADS = 128;
   constexpr int W_BYTES = BN * 128, X_ROWS = NT * 8, X_BYTES = X_ROWS * 128, STAGE_BYTES = W_BYTES + X_BYTES;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -391,7 +417,7 @@ __global__ void __launch_bounds__(128) moe_product_mma_kernel(const bf16* __rest
         if (f >= n_out) continue;
         const float v = acc[j][2 * h + r];
         if (UP)
-          act[(size_t)dst[t] * n_out + f] = __float2bfloat16_rn(gelu_erf(v));
+          act[(size_t)dst[t] * n_out + f] = __float2bfloat16_rn(expert_act(v, act_kind));
         else
           y[(size_t)dst[t] * n_out + f] = v;
       }
@@ -401,23 +427,23 @@ __global__ void __launch_bounds__(128) moe_product_mma_kernel(const bf16* __rest
 
 template <int NT, int STAGES, bool UP>
 int launch_mma(const bf16* a, long long a_stride, const bf16* w, const int* order, const int* tiles, const int* meta, int top, int K,
-               int n_out, int max_tiles, bf16* act, float* y, cudaStream_t st) {
+               int n_out, int max_tiles, bf16* act, float* y, int act_kind, cudaStream_t st) {
   const size_t smem = (size_t)STAGES * (64 * 128 + NT * 8 * 128);
   auto kern = moe_product_mma_kernel<NT, STAGES, UP>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch(kern, dim3((n_out + 63) / 64, max_tiles), dim3(128), smem, st, a, a_stride, w, order, tiles, meta, top, K, n_out, act, y);
+  return launch(kern, dim3((n_out + 63) / 64, max_tiles), dim3(128), smem, st, a, a_stride, w, order, tiles, meta, top, K, n_out, act, y, act_kind);
 }
 
 template <bool UP>
 int product_mma(int tm, const bf16* a, long long a_stride, const bf16* w, const int* order, const int* tiles, const int* meta, int top, int K,
-                int n_out, int max_tiles, bf16* act, float* y, cudaStream_t st) {
-  if (tm <= 8) return launch_mma<1, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, st);
-  if (tm <= 16) return launch_mma<2, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, st);
-  if (tm <= 32) return launch_mma<4, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, st);
-  return launch_mma<8, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, st);
+                int n_out, int max_tiles, bf16* act, float* y, int act_kind, cudaStream_t st) {
+  if (tm <= 8) return launch_mma<1, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, act_kind, st);
+  if (tm <= 16) return launch_mma<2, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, act_kind, st);
+  if (tm <= 32) return launch_mma<4, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, act_kind, st);
+  return launch_mma<8, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, act_kind, st);
 }
 
 // Rows of a tile for P pairs over E experts on the tensor cores: small tiles while an expert has a few rows (the
@@ -487,45 +513,45 @@ KVF_API int kvf_moe_max_tiles(int n_pairs, int E) { return n_pairs / TM_MIN + E;
 
 template <typename T>
 int run_products(const T* x, long long x_stride, const T* w_up, const T* w_down, const int* ids, int P, int W, int ff, int E, int top,
-                 int* order, int* tiles, int* meta, T* act, float* y, cudaStream_t st);
+                 int* order, int* tiles, int* meta, T* act, float* y, int act_kind, cudaStream_t st);
 
 template <>
 int run_products<float>(const float* x, long long x_stride, const float* w_up, const float* w_down, const int* ids, int P, int W, int ff,
-                        int E, int top, int* order, int* tiles, int* meta, float* act, float* y, cudaStream_t st) {
+                        int E, int top, int* order, int* tiles, int* meta, float* act, float* y, int act_kind, cudaStream_t st) {
   int rc = launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), st, ids, P, E, TM, order, tiles, meta);
   if (rc) return rc;
   const int max_tiles = P / TM + E;
   rc = launch(moe_product_kernel<float, true>, dim3((ff + 63) / 64, max_tiles), dim3(256), 0, st, x, x_stride, w_up, (const int*)order,
-              (const int*)tiles, (const int*)meta, top, W, ff, act, (float*)nullptr);
+              (const int*)tiles, (const int*)meta, top, W, ff, act, (float*)nullptr, act_kind);
   if (rc) return rc;
   return launch(moe_product_kernel<float, false>, dim3((W + 63) / 64, max_tiles), dim3(256), 0, st, (const float*)act, (long long)ff,
-                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (float*)nullptr, y);
+                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (float*)nullptr, y, act_kind);
 }
 
 template <>
 int run_products<bf16>(const bf16* x, long long x_stride, const bf16* w_up, const bf16* w_down, const int* ids, int P, int W, int ff, int E,
-                       int top, int* order, int* tiles, int* meta, bf16* act, float* y, cudaStream_t st) {
+                       int top, int* order, int* tiles, int* meta, bf16* act, float* y, int act_kind, cudaStream_t st) {
   const bool tensor = (W % 8 == 0) && (ff % 8 == 0) && (x_stride % 8 == 0) && ((((uintptr_t)x) & 15) == 0);
   const int tm = tensor ? mma_tile_rows(P, E) : TM;
   int rc = launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), st, ids, P, E, tm, order, tiles, meta);
   if (rc) return rc;
   const int max_tiles = P / tm + E;
   if (tensor) {
-    rc = product_mma<true>(tm, x, x_stride, w_up, order, tiles, meta, top, W, ff, max_tiles, act, nullptr, st);
+    rc = product_mma<true>(tm, x, x_stride, w_up, order, tiles, meta, top, W, ff, max_tiles, act, nullptr, act_kind, st);
     if (rc) return rc;
-    return product_mma<false>(tm, act, (long long)ff, w_down, order, tiles, meta, top, ff, W, max_tiles, nullptr, y, st);
+    return product_mma<false>(tm, act, (long long)ff, w_down, order, tiles, meta, top, ff, W, max_tiles, nullptr, y, act_kind, st);
   }
   rc = launch(moe_product_kernel<bf16, true>, dim3((ff + 63) / 64, max_tiles), dim3(256), 0, st, x, x_stride, w_up, (const int*)order,
-              (const int*)tiles, (const int*)meta, top, W, ff, act, (float*)nullptr);
+              (const int*)tiles, (const int*)meta, top, W, ff, act, (float*)nullptr, act_kind);
   if (rc) return rc;
   return launch(moe_product_kernel<bf16, false>, dim3((W + 63) / 64, max_tiles), dim3(256), 0, st, (const bf16*)act, (long long)ff,
-                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (bf16*)nullptr, y);
+                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (bf16*)nullptr, y, act_kind);
 }
 
 #define KVF_EXPERTS_API(SUF, T)                                                                                       \
   KVF_API int kvf_moe_route_##SUF(const void* x, long long x_stride, const float* router, const float* correction,    \
                                   int n_tokens, int W, int E, int top, int groups, int keep, float norm_eps,          \
-                                  int* ids, float* wts, cudaStream_t st) {                                            \
+                                  int flags, int* ids, float* wts, cudaStream_t st) {                                 \
     if (n_tokens <= 0) return 0;                                                                                      \
     if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||                   \
         top > keep * (E / groups))                                                                                    \
@@ -536,20 +562,20 @@ int run_products<bf16>(const bf16* x, long long x_stride, const bf16* w_up, cons
     const int vec = (W % 8 == 0) && (x_stride % 8 == 0) && ((((uintptr_t)x) | ((uintptr_t)router)) % 16 == 0);        \
     if (rt == 1)                                                                                                      \
       return launch(moe_route_kernel<T, 1>, dim3(n_tokens), dim3(256), smem, st, (const T*)x, x_stride, router,       \
-                    correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, ids, wts);                          \
+                    correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, flags, ids, wts);                   \
     return launch(moe_route_kernel<T, 4>, dim3((n_tokens + 3) / 4), dim3(256), smem, st, (const T*)x, x_stride,       \
-                  router, correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, ids, wts);                    \
+                  router, correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, flags, ids, wts);             \
   }                                                                                                                   \
   KVF_API int kvf_moe_experts_##SUF(const void* x, long long x_stride, const void* w_up, const void* w_down,          \
                                     const int* ids, const float* wts, int n_tokens, int W, int ff, int E, int top,    \
                                     int* order, int* tiles, int* meta, void* act, float* y, float* resid,             \
-                                    cudaStream_t st) {                                                                \
+                                    int act_kind, cudaStream_t st) {                                                  \
     if (n_tokens <= 0) return 0;                                                                                      \
     const int P = n_tokens * top;                                                                                     \
     if ((size_t)3 * E * sizeof(int) > 48 * 1024) return (int)cudaErrorInvalidValue;                                   \
     if (kvf_moe_max_tiles(P, E) > 65535) return (int)cudaErrorInvalidValue;                                           \
     int rc = run_products<T>((const T*)x, x_stride, (const T*)w_up, (const T*)w_down, ids, P, W, ff, E, top, order,   \
-                             tiles, meta, (T*)act, y, st);                                                            \
+                             tiles, meta, (T*)act, y, act_kind, st);                                                  \
     if (rc) return rc;                                                                                                \
     const long long total = (long long)n_tokens * W;                                                                  \
     long long g = (total + 255) / 256;                                                                                \

@@ -44,7 +44,7 @@ struct TcParams {
   void* out;
   int M, N, K;
   int ldo;
-  int mode;  // 0: bfloat16 y; 3: bfloat16 silu(g)*u; 4: bfloat16 gelu(y); 5: float y to the rows that `scatter` names
+  int mode;  // 0: bfloat16 y; 3: bfloat16 silu(g)*u; 4: bfloat16 gelu(y); 5: float y to the rows that `scatter` names; 6: bfloat16 relu(y)^2
   int* err;
   // grouped form: `tiles` holds (expert, first row, rows) per row tile, meta[0] their number (at most max_row_tiles);
   // N is then the number of output columns of ONE expert
@@ -299,6 +299,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             r[i] = __float_as_uint(0.5f * z * (1.f + erff(z * 0.70710678118654752440f)));
           }
         }
+        if (p.mode == 6) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float z = fmaxf(__uint_as_float(r[i]), 0.f);
+            r[i] = __float_as_uint(z * z);
+          }
+        }
         if (p.mode == 3) {
           // columns are weight rows [g0..7, u0..7, g8..15, u8..15]: 16 outputs from 32 columns
           bf16* dst = reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldo + (col >> 1);
@@ -429,7 +436,7 @@ KVF_API int kvf_gemm_tcgen05_bf16(const void* x, const void* w, void* out, int M
 
 // The grouped form: x [P, K] with its rows ordered by expert, w [E * N, K], `tiles` / `meta` as a sort on the device
 // left them (row tiles of at most 128 rows, at most max_row_tiles of them).  gelu != 0: out bfloat16 [P, N] =
-// gelu(x w[e]^T) in the order of x; else out float, row i of the product going to row scatter[i] ([*, N]).
+// act(x w[e]^T) in the order of x (1: the exact GELU, 2: the square of relu); else out float, row i of the product going to row scatter[i] ([*, N]).
 KVF_API int kvf_gemm_grouped_tcgen05_bf16(const void* x, const void* w, void* out, int P, int N, int K, int E, int ldx,
                                           int ldo, int gelu, const int* tiles, const int* meta, const int* scatter,
                                           int max_row_tiles, int* err, cudaStream_t st) {
@@ -438,7 +445,7 @@ KVF_API int kvf_gemm_grouped_tcgen05_bf16(const void* x, const void* w, void* ou
   if ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) return (int)cudaErrorInvalidValue;
   if ((long long)E * N > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
   TcParams p;
-  p.out = out; p.M = P; p.N = N; p.K = K; p.ldo = ldo; p.mode = gelu ? 4 : 5; p.err = err;
+  p.out = out; p.M = P; p.N = N; p.K = K; p.ldo = ldo; p.mode = gelu == 2 ? 6 : gelu ? 4 : 5; p.err = err;
   p.tiles = tiles; p.meta = meta; p.scatter = gelu ? nullptr : scatter; p.max_row_tiles = max_row_tiles;
   CUtensorMap mx, mw;
   int rc = make_map(&mx, x, P, K, ldx, BM);

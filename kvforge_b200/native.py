@@ -42,6 +42,9 @@ LIBRARIES: dict[str, tuple[list[str], list[str]]] = {
     # attention layers with normed heads or latent keys and values, and the feed-forward of routed experts; a
     # library of its own for the same reason
     "routed": (["head_ops.cu", "experts.cu"], []),
+    # layers whose sublayer results are gated and normed before they join the residual stream, heads that are
+    # rotated and then normed, attention whose heads talk before the softmax; a library of its own for the same reason
+    "gated": (["gated_ops.cu", "attention_talking_f32.cu", "attention_talking_bf16.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -38,6 +38,7 @@ _SIGNATURES = {
     "kvf_gemm_tcgen05_bf16": "pppiiiiiiipp",
     "kvf_sample_f32": "pliippppppp",
     "kvf_argmax_f32": "pliipipp",
+    "kvf_scale_softcap_f32": "plffp",
     # library "mixers"
     "kvf_causal_conv_{s}": "pipplppiiiiipiip",
     "kvf_gated_delta_{s}": "pppipipippiplpippiiiiiffiippppilp",
@@ -53,14 +54,20 @@ _SIGNATURES = {
     "kvf_latent_prepare_{s}": "pliippfpipppiiiiiilpp",
     "kvf_head_gate_{s}": "pplliip",
     "kvf_add_row_f32": "pplip",
-    "kvf_moe_route_{s}": "plppiiiiiifppp",
-    "kvf_moe_experts_{s}": "plppppiiiiippppppp",
+    "kvf_moe_route_{s}": "plppiiiiiifippp",
+    "kvf_moe_experts_{s}": "plppppiiiiippppppip",
     "kvf_moe_max_tiles": "ii",
     "kvf_moe_sort": "piiipppp",
     "kvf_moe_gather_bf16": "plpiiipp",
     "kvf_moe_combine": "pppiiip",
     "kvf_gemm_grouped_tcgen05_bf16": "pppiiiiiiipppipp",
     "kvf_routed_set_pdl": "i",
+    # library "gated"
+    "kvf_norm_step_{s}": "pppplliplppppliiiifp",
+    "kvf_qk_prepare_{s}": "pliiippiifpppiiiiiilpp",
+    "kvf_unary_act_{s}": "plplliipp",
+    "kvf_talking_attention_{s}": "pppppppppiiiiiiiiiifiiiippp",
+    "kvf_gated_set_pdl": "i",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 
@@ -140,7 +147,7 @@ def set_pdl(enabled: bool) -> None:
 
 
 # every shared library has a flag of its own; it follows the core's once the library is loaded
-_PDL_SETTERS = {"mixers": "kvf_mixers_set_pdl", "routed": "kvf_routed_set_pdl"}
+_PDL_SETTERS = {"mixers": "kvf_mixers_set_pdl", "routed": "kvf_routed_set_pdl", "gated": "kvf_gated_set_pdl"}
 _library_pdl: dict[str, bool] = {}
 
 
@@ -1494,13 +1501,14 @@ def moe_max_tiles(n_pairs: int, num_experts: int) -> int:
 
 def moe_route(
     x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int, keep: int, norm_eps: float,
-    ids: torch.Tensor, weights: torch.Tensor,
+    ids: torch.Tensor, weights: torch.Tensor, softmax: bool = False, normalize: bool = True,
 ) -> None:  # fmt: skip
     """Per token of ``x [N, W]``: logits ``router [E, W] x`` in float, scores ``s = sigmoid(z)``; the ``top``
     experts with the largest ``s + correction`` among the best ``keep`` of ``groups`` equal groups of
     neighbouring experts (a group's rank: the sum of the top two ``s + correction`` among its members) are chosen
     (``ids`` int32 ``[N, top]``); their weights are their ``s`` over the sum of those (+ ``norm_eps``)
-    (``weights`` float ``[N, top]``)."""
+    (``weights`` float ``[N, top]``).  ``softmax``: the scores are ``softmax(z)`` over all experts instead;
+    ``normalize=False``: the weights are the chosen scores as they are."""
     s = _suffix(x.dtype)
     _rows2d(x, None, "x")
     _need(router, torch.float32, "router")
@@ -1518,11 +1526,12 @@ def moe_route(
         raise ValueError("moe_route: ids and weights must be [N, top]")
     name = f"kvf_moe_route_{s}"
     _check(
-        _fn(name, ROUTED_LIB)(_ptr(x), x.stride(0), _ptr(router), _ptr(correction), n, w, e, int(top), int(groups), int(keep), float(norm_eps), _ptr(ids), _ptr(weights), _stream()),
+        _fn(name, ROUTED_LIB)(_ptr(x), x.stride(0), _ptr(router), _ptr(correction), n, w, e, int(top), int(groups), int(keep), float(norm_eps), (1 if softmax else 0) | (0 if normalize else 2), _ptr(ids), _ptr(weights), _stream()),
         name,
     )
 
 
+EXPERT_ACTIVATIONS = {"gelu": 0, "relu2": 1}  # what the experts' kernels apply between their two products
 GROUPED_TILE_ROWS = 128  # rows of a tile of the tensor-memory product
 # from this many rows an expert (on average) the two products of routed experts run on the tcgen05 tensor cores
 GROUPED_TCGEN05_MIN_ROWS = 64
@@ -1530,15 +1539,19 @@ GROUPED_TCGEN05_MIN_ROWS = 64
 
 def moe_experts(
     x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, scratch: dict, resid: torch.Tensor,
-    err: torch.Tensor | None = None,
+    err: torch.Tensor | None = None, activation: str = "gelu",
 ) -> None:  # fmt: skip
-    """``resid[n] += sum_k weights[n, k] * w_down[e] gelu(w_up[e] x[n])`` with ``e = ids[n, k]``: the pairs are
+    """``resid[n] += sum_k weights[n, k] * w_down[e] act(w_up[e] x[n])`` with ``e = ids[n, k]`` and ``act`` the exact
+    GELU (``"gelu"``) or the square of relu (``"relu2"``): the pairs are
     ordered by expert, every expert's rows go through its two products in tiles, and the results are
     summed per token in the order of ``k``.  ``w_up [E, ff, W]``, ``w_down [E, W, ff]``; ``scratch``: ``order``
     int32 ``[N*top]``, ``tiles`` int32 ``[3*max_tiles]``, ``meta`` int32 ``[4]``, ``act [N*top, ff]``, ``y`` float
     ``[N*top, W]``, and for many bfloat16 rows ``xs [N*top, W]`` (the pairs' rows side by side by expert).  Four
     launches, five through the tensor-memory product (``err``: the device flag its bounded waits raise)."""
     s = _suffix(x.dtype)
+    if activation not in EXPERT_ACTIVATIONS:
+        raise ValueError(f"moe_experts: activation {activation!r} is not one of {sorted(EXPERT_ACTIVATIONS)}")
+    act_kind = EXPERT_ACTIVATIONS[activation]
     _rows2d(x, None, "x")
     _need(w_up, x.dtype, "w_up")
     _need(w_down, x.dtype, "w_down")
@@ -1570,7 +1583,7 @@ def moe_experts(
         _check(_fn("kvf_moe_sort", ROUTED_LIB)(_ptr(ids), pairs, e, GROUPED_TILE_ROWS, _ptr(order), _ptr(tiles), _ptr(meta), st), "kvf_moe_sort")
         _check(_fn("kvf_moe_gather_bf16", ROUTED_LIB)(_ptr(x), x.stride(0), _ptr(order), top, pairs, w, _ptr(xs), st), "kvf_moe_gather_bf16")
         g = _fn("kvf_gemm_grouped_tcgen05_bf16")
-        _check(g(_ptr(xs), _ptr(w_up), _ptr(act), pairs, ff, w, e, w, ff, 1, _ptr(tiles), _ptr(meta), None, row_tiles, _ptr(err), st), "kvf_gemm_grouped_tcgen05_bf16")
+        _check(g(_ptr(xs), _ptr(w_up), _ptr(act), pairs, ff, w, e, w, ff, 1 + act_kind, _ptr(tiles), _ptr(meta), None, row_tiles, _ptr(err), st), "kvf_gemm_grouped_tcgen05_bf16")
         _check(g(_ptr(act), _ptr(w_down), _ptr(y), pairs, w, ff, e, ff, w, 0, _ptr(tiles), _ptr(meta), _ptr(order), row_tiles, _ptr(err), st), "kvf_gemm_grouped_tcgen05_bf16")
         _check(_fn("kvf_moe_combine", ROUTED_LIB)(_ptr(resid), _ptr(y), _ptr(weights), n, w, top, st), "kvf_moe_combine")
         return
@@ -1578,8 +1591,226 @@ def moe_experts(
     _check(
         _fn(name, ROUTED_LIB)(
             _ptr(x), x.stride(0), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), n, w, ff, e, top, _ptr(order), _ptr(tiles), _ptr(meta),
-            _ptr(act), _ptr(y), _ptr(resid), _stream(),
+            _ptr(act), _ptr(y), _ptr(resid), act_kind, _stream(),
         ),
         name,
         4,
+    )  # fmt: skip
+
+
+# ------------------------------------------------------------------ library "gated"
+# gated and normed sublayer results, rotation followed by a head norm, attention whose heads talk
+
+GATED_LIB = "gated"
+
+
+@dataclass
+class GatedWrite:
+    """A sublayer's result that is still to be gated, normed and added to the residual stream:
+    ``resid += norm(y * sigmoid(z + z_bias)) * post_w``.  ``y``: a tensor in the storage type or the
+    ``Partials`` of a split product; ``z``: gate logits in the storage type ``[N, W]`` (a view with a row
+    stride of its own is fine) or ``None`` (no gate); ``post_w``: float ``[W]`` or ``None`` (added as it is).
+    The norm that consumes it decides the norm's kind and eps: the same as its own."""
+
+    y: "torch.Tensor | Partials"
+    z: torch.Tensor | None = None
+    z_bias: torch.Tensor | None = None
+    post_w: torch.Tensor | None = None
+
+
+def norm_step(
+    resid: torch.Tensor,
+    pending,
+    next_w: torch.Tensor | None,
+    out: torch.Tensor | None,
+    eps: float,
+    centred: bool = True,
+    rows: torch.Tensor | None = None,
+    store_normed: bool = False,
+) -> None:
+    """One pass over every row of the float residual stream ``resid [N, W]``:
+
+    * ``pending`` (``None``, ``ADDED``, a tensor, ``Partials`` or a ``GatedWrite``) is gated, normed and added
+      (the sum is written back unless ``rows`` picks rows);
+    * ``out`` (storage type, rows may be a view of a wider buffer) gets the row normed with ``next_w``
+      (``None``: the row itself); with ``store_normed`` the normed row also replaces the residual row.
+
+    The norm is the layer norm ``(x - mean) / sqrt(var + eps) * w`` with the variance of the deviations
+    (``centred``), or the RMS norm ``x / sqrt(mean(x^2) + eps) * w``."""
+    _need(resid, torch.float32, "resid")
+    w = resid.shape[-1]
+    if pending is ADDED:
+        pending = None
+    gw = pending if isinstance(pending, GatedWrite) else GatedWrite(pending) if pending is not None else None
+    if out is not None:
+        s = _suffix(out.dtype)
+        _need(out, None, "out", contiguous=False)
+        if out.dim() != 2 or out.stride(1) != 1 or out.shape[1] != w:
+            raise ValueError("norm_step: out must be [rows, W] with unit inner stride")
+        n_rows, optr, ostride = out.shape[0], _ptr(out), out.stride(0)
+    else:
+        n_rows, optr, ostride = resid.shape[0], None, 0
+        s = None
+    yptr = pptr = zptr = None
+    ystride = sstride = zstride = nsplit = 0
+    if gw is not None:
+        if isinstance(gw.y, Partials):
+            _need(gw.y.t, torch.float32, "partials", contiguous=False)
+            if gw.y.t.shape[-1] != w or gw.y.t.stride(1) != w or gw.y.t.stride(2) != 1:
+                raise ValueError("norm_step: partials must be [S, M, W] with dense rows")
+            pptr, nsplit, sstride = _ptr(gw.y.t), gw.y.nsplit, gw.y.split_stride
+        else:
+            _need(gw.y, None, "pending result", contiguous=False)
+            if gw.y.dim() != 2 or gw.y.stride(1) != 1 or gw.y.shape[1] != w:
+                raise ValueError("norm_step: the pending result must be [N, W] with unit inner stride")
+            if s is not None and _suffix(gw.y.dtype) != s:
+                raise TypeError("norm_step: the pending result and out must have the storage type")
+            s = _suffix(gw.y.dtype)
+            yptr, ystride = _ptr(gw.y), gw.y.stride(0)
+        if gw.z is not None:
+            _need(gw.z, None, "gate logits", contiguous=False)
+            if gw.z.dim() != 2 or gw.z.stride(1) != 1 or gw.z.shape[1] != w:
+                raise ValueError("norm_step: gate logits must be [N, W] with unit inner stride")
+            if s is not None and _suffix(gw.z.dtype) != s:
+                raise TypeError("norm_step: gate logits must have the storage type")
+            s = _suffix(gw.z.dtype)
+            zptr, zstride = _ptr(gw.z), gw.z.stride(0)
+        for t, what in ((gw.z_bias, "gate bias"), (gw.post_w, "post-norm weight")):
+            if t is not None:
+                _need(t, torch.float32, what)
+                if t.numel() != w:
+                    raise ValueError(f"norm_step: {what} must have W entries")
+    if next_w is not None:
+        _need(next_w, torch.float32, "norm weight")
+        if next_w.numel() != w:
+            raise ValueError("norm_step: norm weight must have W entries")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        if rows.numel() < n_rows:
+            raise ValueError("norm_step: fewer row indices than output rows")
+    elif resid.shape[0] < n_rows:
+        raise ValueError("norm_step: fewer residual rows than output rows")
+    name = f"kvf_norm_step_{s or 'f32'}"
+    _check(
+        _fn(name, GATED_LIB)(
+            _ptr(resid), _ptr(rows), yptr, pptr, ystride, sstride, nsplit, zptr, zstride,
+            _ptr(gw.z_bias) if gw else None, _ptr(gw.post_w) if gw else None, _ptr(next_w), optr, ostride,
+            n_rows, w, 1 if centred else 0, 1 if store_normed else 0, float(eps), _stream(),
+        ),
+        name,
+    )  # fmt: skip
+
+
+def qk_prepare(
+    x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, norm_eps: float | None, slots: torch.Tensor,
+    kcache: torch.Tensor, vcache: torch.Tensor, nh: int, nkv: int, d: int, dv: int, k_off: int, v_off: int, v_step: int,
+    block_size: int, err: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """Rows of ``x`` hold ``nh`` query heads of ``d`` from column 0, ``nkv`` key heads from column ``k_off`` and
+    the value heads' sources from column ``v_off`` (``v_step`` apart, the first ``dv`` numbers of each).  The
+    values go to their slots as they are.  The first ``2 * len(inv_freq)`` dims of every query and key head turn
+    in split pairs ``(i, i + rot/2)`` by ``pos * inv_freq[i]``; then, unless ``norm_eps`` is ``None``, the head is
+    divided by ``sqrt(mean(x^2) + norm_eps)``.  Queries are written back in place, keys to their slots."""
+    s = _suffix(x.dtype)
+    _rows2d(x, None, "x")
+    _need(positions, torch.int32, "positions")
+    _need(inv_freq, torch.float32, "inv_freq")
+    _need(slots, torch.int32, "slots")
+    _need(kcache, x.dtype, "kcache")
+    _need(vcache, x.dtype, "vcache")
+    n = x.shape[0]
+    rot = 2 * inv_freq.numel()
+    if rot > d or tuple(kcache.shape[1:]) != (nkv, block_size, d) or tuple(vcache.shape[1:]) != (nkv, block_size, dv) or kcache.shape[0] != vcache.shape[0]:
+        raise ValueError("qk_prepare: cache shapes must be [blocks, nkv, block_size, d] and [..., dv], and rot <= d")
+    if k_off < nh * d or k_off + nkv * d > x.shape[1] or v_off + (nkv - 1) * v_step + dv > x.shape[1] or positions.numel() < n or slots.numel() < n:
+        raise ValueError("qk_prepare: the rows do not hold what the offsets say")
+    name = f"kvf_qk_prepare_{s}"
+    _check(
+        _fn(name, GATED_LIB)(
+            _ptr(x), x.stride(0), int(k_off), int(v_off), int(v_step), _ptr(positions), _ptr(inv_freq), rot, 0 if norm_eps is None else 1,
+            float(norm_eps or 0.0), _ptr(slots), _ptr(kcache), _ptr(vcache), n, nh, nkv, d, dv, block_size, kcache.shape[0] * block_size,
+            _ptr(err), _stream(),
+        ),
+        name,
+    )  # fmt: skip
+
+
+UNARY_ACTIVATIONS = {"xielu": 0, "relu2": 1, "gelu_tanh": 2}
+
+
+def unary_act(x: torch.Tensor, out: torch.Tensor, kind: str, ab: torch.Tensor | None = None) -> None:
+    """``out = act(x)`` row by row in float, rounded once.  ``xielu`` with the two numbers ``ab = (p, q)``:
+    ``z > 0: softplus(p) z^2 + z/2``, ``z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2``; ``relu2``:
+    ``relu(z)^2``; ``gelu_tanh``: ``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``."""
+    s = _suffix(x.dtype)
+    _rows2d(x, None, "x")
+    _rows2d(out, x.dtype, "out")
+    if kind not in UNARY_ACTIVATIONS or out.shape != x.shape:
+        raise ValueError("unary_act: unknown activation or shapes differ")
+    if kind == "xielu":
+        _need(ab, torch.float32, "xielu parameters")
+        if ab.numel() != 2:
+            raise ValueError("unary_act: xielu takes two numbers")
+    name = f"kvf_unary_act_{s}"
+    _check(_fn(name, GATED_LIB)(_ptr(x), x.stride(0), _ptr(out), out.stride(0), x.shape[0], x.shape[1], UNARY_ACTIVATIONS[kind], _ptr(ab), _stream()), name)
+
+
+def scale_softcap(logits: torch.Tensor, scale: float, cap: float) -> None:
+    """``logits <- cap * tanh(scale * logits / cap)`` in place (``cap == 0``: ``scale * logits``)."""
+    _need(logits, torch.float32, "logits")
+    name = "kvf_scale_softcap_f32"
+    _check(_fn(name)(_ptr(logits), logits.numel(), float(scale), float(cap), _stream()), name)
+
+
+TALKING_MAX_HEADS = 64  # what the kernel's CTA of eight warps holds: a row per (head, query), eight rows a warp
+
+
+def talking_attention(
+    q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+    query_start_loc: torch.Tensor, context_lens: torch.Tensor, num_seqs: int, max_query_len: int, nh: int, nkv: int, d: int, dv: int,
+    scale: float, talk: torch.Tensor | None, sink: torch.Tensor | None, q_stride: int | None = None, window: int = 0,
+    scratch: tuple | None = None, max_context: int | None = None, split_size: int = 256,
+) -> None:  # fmt: skip
+    """Causal attention over the paged cache whose heads' scores are mixed before the softmax
+    (``s'_h = sum_g talk[h, g] s_g``, ``talk`` float ``[nh, nh]`` or ``None``) and whose softmax may have a sink
+    (``sink`` float ``[nh]``: ``exp(sink_h)`` joins the denominator, with no key and no value).  ``q`` rows hold
+    ``nh`` heads of ``d`` (row stride ``q_stride``), ``out [N, nh * dv]``; ``scratch``: the decode form (every
+    sequence one query; key ranges of ``split_size`` in parallel, then a merge) with ``(part_acc, part_ml, _)``
+    as ``attention_scratch_shapes`` gives them."""
+    s = _suffix(q.dtype)
+    _need(q, None, "q", contiguous=False)
+    _need(out, q.dtype, "out")
+    _need(kcache, q.dtype, "kcache")
+    _need(vcache, q.dtype, "vcache")
+    for t, what in ((block_tables, "block_tables"), (query_start_loc, "query_start_loc"), (context_lens, "context_lens")):
+        _need(t, torch.int32, what)
+    block_size = kcache.shape[2]
+    if tuple(kcache.shape[1:]) != (nkv, block_size, d) or tuple(vcache.shape[1:]) != (nkv, block_size, dv) or out.shape[1] != nh * dv:
+        raise ValueError("talking_attention: cache or output shape")
+    if nh > TALKING_MAX_HEADS:
+        raise ValueError(f"talking_attention: at most {TALKING_MAX_HEADS} heads")
+    for t, shape, what in ((talk, (nh, nh), "talk"), (sink, (nh,), "sink")):
+        if t is not None:
+            _need(t, torch.float32, what)
+            if tuple(t.shape) != shape:
+                raise ValueError(f"talking_attention: {what} must be {shape}")
+    acc = ml = None
+    split = max_splits = grid_splits = 0
+    if scratch is not None:
+        acc, ml = scratch[0], scratch[1]
+        split = int(split_size)
+        max_splits = acc.shape[2]
+        bound = max(int(max_context or 0), 1)
+        grid_splits = min(max_splits, -(-bound // split))
+        if acc.shape[0] < num_seqs or acc.shape[1] != nh or acc.shape[3] != dv or -(-bound // split) > max_splits:
+            raise ValueError("talking_attention: scratch too small for this step")
+    name = f"kvf_talking_attention_{s}"
+    _check(
+        _fn(name, GATED_LIB)(
+            _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(query_start_loc), _ptr(context_lens), _ptr(talk), _ptr(sink),
+            int(num_seqs), int(max_query_len), int(q_stride or q.stride(0)), out.stride(0), block_tables.stride(0), nh, nkv, d, dv, block_size,
+            float(scale), int(window), split, max_splits, grid_splits, _ptr(acc), _ptr(ml), _stream(),
+        ),
+        name,
+        2 if scratch is not None else 1,
     )  # fmt: skip

@@ -166,3 +166,104 @@ class StreamPreNormBlock(Block):
         finally:
             ctx.residual = keep
         return pending
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """A norm before and after each sublayer, and a gate on the sublayer's result:
+    ``h = norm1(x); x = x + norm1b(mixer(h) * sigmoid(W_g1 h + b_g1))`` and the same with the feed-forward
+    (``norm2``, ``norm2b``, ``W_g2``, ``b_g2``).  The gate, the norm after the sublayer and the residual sum are
+    folded into the kernel of the norm that follows (an ``ops.GatedWrite`` is what the block hands on).
+
+    params: ``hidden_size``, ``norm`` (the ``PartSpec`` of all four norms, e.g. ``layernorm``), ``mixer``, ``ffn``
+    (``PartSpec``; ``ffn`` may be ``None``), ``gate`` (default true: the tensors ``<gate1_name> [W, W]`` and
+    ``<gate1_name>.b [W]``, and the same for the feed-forward), and the names ``norm1_name``, ``norm1_post_name``,
+    ``norm2_name``, ``norm2_post_name``, ``mixer_name``, ``ffn_name``, ``gate1_name``, ``gate2_name`` under the
+    layer's prefix.  A sublayer that can take further rows into its input product (``stack_input``) computes the
+    gate's logits there; otherwise the block runs the product itself."""
+
+    DEFAULT_NAMES = {
+        "norm1_name": "norm1", "norm1_post_name": "norm1b", "norm2_name": "norm2", "norm2_post_name": "norm2b",
+        "mixer_name": "mix", "ffn_name": "mlp", "gate1_name": "rg1", "gate2_name": "rg2",
+    }  # fmt: skip
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden_size"])
+        nm = {k: params.get(k, v) for k, v in self.DEFAULT_NAMES.items()}
+        self.names = nm
+        self.gated = bool(params.get("gate", True))
+        self.gates = [None, None]
+        norm = _spec(params["norm"])
+
+        def named_norm(name):
+            return build_part("norm", PartSpec(norm.kind, {**norm.params, "names": {"weight": name}}), prefix)
+
+        self.norm1, self.norm1_post = named_norm(nm["norm1_name"]), named_norm(nm["norm1_post_name"])
+        self.mixer = build_part("mixer", _spec(params["mixer"]), _stem(prefix, nm["mixer_name"]))
+        self.ffn = self.norm2 = self.norm2_post = None
+        if params.get("ffn") is not None:
+            self.norm2, self.norm2_post = named_norm(nm["norm2_name"]), named_norm(nm["norm2_post_name"])
+            self.ffn = build_part("ffn", _spec(params["ffn"]), _stem(prefix, nm["ffn_name"]))
+
+    @classmethod
+    def weight_decls(cls, params):
+        if not params.get("gate", True):
+            return {}
+        w = int(params["hidden_size"])
+        out = {}
+        for key in ("gate1_name", "gate2_name"):
+            if key == "gate2_name" and params.get("ffn") is None:
+                continue
+            stem = params.get(key, cls.DEFAULT_NAMES[key])
+            out[stem] = WeightDecl((w, w))
+            out[f"{stem}.b"] = WeightDecl((w,), kind="vector", init="zeros")
+        return out
+
+    def sub_parts(self):
+        return [p for p in (self.norm1, self.norm1_post, self.mixer, self.norm2, self.norm2_post, self.ffn) if p is not None]
+
+    def mixer_part(self):
+        return self.mixer
+
+    def bind(self, weights, rt):
+        super().bind(weights, rt)
+        self.gates = []  # per sublayer: (matrix or None when the sublayer computes the logits, bias)
+        for key, part in (("gate1_name", self.mixer), ("gate2_name", self.ffn)):
+            if part is None or not self.gated:
+                self.gates.append(None)
+                continue
+            stem = self.names[key]
+            w, b = weights[stem].contiguous(), weights[f"{stem}.b"].contiguous()
+            stacked = bool(getattr(part, "stack_input", None)) and part.stack_input(w)
+            self.gates.append((None if stacked else w, b))
+
+    def _gate(self, ctx, which: int, part, x):
+        g = self.gates[which]
+        if g is None:
+            return None, None
+        w, b = g
+        if w is None:
+            return part.extra_out, b
+        z = self.rt.buf(f"block.gate{which}", x.shape[0], self.hidden)
+        if ops.skinny_ok(x, w):
+            ops.gemm_skinny(x, w, z)
+        else:
+            ops.linear(x, w, z)
+        return z, b
+
+    def forward(self, ctx, resid, delta, cache):
+        keep, ctx.residual = ctx.residual, None  # a result is gated and normed before it joins the stream
+        try:
+            x = self.norm1.forward(ctx, resid, delta)
+            y = self.mixer.forward(ctx, x, cache)
+            z, b = self._gate(ctx, 0, self.mixer, x)
+            pending = ops.GatedWrite(y, z, b, self.norm1_post.weight)
+            if self.ffn is not None:
+                x = self.norm2.forward(ctx, resid, pending)
+                y = self.ffn.forward(ctx, x)
+                z, b = self._gate(ctx, 1, self.ffn, x)
+                pending = ops.GatedWrite(y, z, b, self.norm2_post.weight)
+        finally:
+            ctx.residual = keep
+        return pending

@@ -1,10 +1,11 @@
 """A feed-forward of many small experts of which every token uses a few.
 
 Expert ``e`` is ``W_down[e] act(W_up[e] x)`` without biases.  The router's logits ``z = W_router x``
-and everything made of them are 32-bit: scores ``s = sigmoid(z)``; the choice is made on
-``s + correction`` (a tensor that shifts the choice, not the weights), among the experts of the best
-groups only when the experts form groups; the chosen experts' results are summed with weights
-``s / (sum of the chosen s + 1e-20)``.
+and everything made of them are 32-bit: scores ``s = sigmoid(z)`` (or ``softmax(z)`` over all experts); the
+choice is made on ``s + correction`` (a tensor that shifts the choice, not the weights), among the experts of
+the best groups only when the experts form groups; the chosen experts' results are summed with weights
+``s / (sum of the chosen s + 1e-20)`` (or with the chosen ``s`` as they are).  A shared expert, a feed-forward
+of its own that every token passes, may be added to the sum.
 """
 
 from __future__ import annotations
@@ -12,7 +13,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import FeedForward, WeightDecl, register_feed_forward
+from .base import FeedForward, PartSpec, WeightDecl, build_part, register_feed_forward
 
 WEIGHT_SUM_EPS = 1e-20  # added to the sum of the chosen scores before the division
 
@@ -23,7 +24,10 @@ class RoutedExperts(FeedForward):
     (only ``"gelu"``, the exact one); optional ``groups`` and ``keep`` (the experts form ``groups`` equal
     groups of neighbours; a group is ranked by the sum of the top two shifted scores among its members, and
     only members of the ``keep`` best-ranked groups are eligible) and ``correction`` (default true: the tensor
-    ``correction [experts]`` is added to the scores for the choice).
+    ``correction [experts]`` is added to the scores for the choice), ``activation`` (``"gelu"``, the exact one, or
+    ``"relu2"``, the square of relu), ``score`` (``"sigmoid"`` or ``"softmax"``), ``normalize`` (default true; false:
+    the weights are the chosen scores, not divided by their sum) and ``shared`` (the ``PartSpec`` of a feed-forward
+    that runs for every token and is added; its tensors lie under ``shared.``).
 
     Tensors: ``router [E, W]``, ``correction [E]``, ``e<i>.up [ff, W]``, ``e<i>.down [W, ff]``."""
 
@@ -34,8 +38,17 @@ class RoutedExperts(FeedForward):
         self.groups = int(p.get("groups") or 1)
         self.keep = int(p.get("keep") or self.groups)
         self.corrected = bool(p.get("correction", True))
-        if p.get("activation", "gelu") != "gelu":
-            raise ValueError("the experts' activation is 'gelu'")
+        self.activation = p.get("activation", "gelu")
+        if self.activation not in ops.EXPERT_ACTIVATIONS:
+            raise ValueError(f"the experts' activation is one of {sorted(ops.EXPERT_ACTIVATIONS)}")
+        self.score = p.get("score", "sigmoid")
+        if self.score not in ("sigmoid", "softmax"):
+            raise ValueError("score must be 'sigmoid' or 'softmax'")
+        self.normalize = bool(p.get("normalize", True))
+        shared = p.get("shared")
+        if isinstance(shared, dict):
+            shared = PartSpec(shared["kind"], shared.get("params", {}))
+        self.shared = build_part("ffn", shared, prefix + "shared.") if shared is not None else None
         if not 0 < self.top <= self.experts or self.experts % self.groups or not 0 < self.keep <= self.groups:
             raise ValueError("experts must divide into the groups, and top and keep must be within their counts")
         if self.top > self.keep * (self.experts // self.groups):
@@ -52,6 +65,19 @@ class RoutedExperts(FeedForward):
             out[f"e{i}.down"] = WeightDecl((w, ff))
         return out
 
+    def sub_parts(self):
+        return [self.shared] if self.shared is not None else []
+
+    def stack_input(self, w: torch.Tensor) -> bool:
+        """Further rows for a product that reads this part's input: the shared expert's first product takes them."""
+        if self.shared is None or not getattr(self.shared, "stack_input", None):
+            return False
+        return bool(self.shared.stack_input(w))
+
+    @property
+    def extra_out(self):
+        return self.shared.extra_out
+
     def bind(self, weights, rt):
         super().bind(weights, rt)
         self.router = weights["router"].contiguous()
@@ -66,7 +92,7 @@ class RoutedExperts(FeedForward):
         pairs_cap = rt.max_tokens * top
         ids = rt.buf("experts.ids", n, top, torch.int32)
         wts = rt.buf("experts.weights", n, top, torch.float32)
-        ops.moe_route(x, self.router, self.correction, top, self.groups, self.keep, WEIGHT_SUM_EPS, ids, wts)
+        ops.moe_route(x, self.router, self.correction, top, self.groups, self.keep, WEIGHT_SUM_EPS, ids, wts, self.score == "softmax", self.normalize)
         scratch = {
             "order": rt.buf("experts.order", n * top, 1, torch.int32, cap=pairs_cap),
             "tiles": rt.buf("experts.tiles", ops.moe_max_tiles(n * top, e), 3, torch.int32, cap=ops.moe_max_tiles(pairs_cap, e)),
@@ -78,9 +104,17 @@ class RoutedExperts(FeedForward):
             scratch["xs"] = rt.buf("experts.xs", n * top, self.hidden, cap=pairs_cap)
         resid = getattr(ctx, "residual", None)
         if resid is not None and resid.shape[0] >= n and resid.shape[1] == self.hidden:
-            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, resid[:n], rt.err)
-            return ops.ADDED
+            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, resid[:n], rt.err, self.activation)
+            return self.shared.forward(ctx, x) if self.shared is not None else ops.ADDED
         out = rt.buf("experts.out", n, self.hidden, torch.float32)
         out.zero_()
-        ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out, rt.err)
+        ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out, rt.err, self.activation)
+        if self.shared is not None:
+            # the shared expert's result joins the routed sum in 32-bit
+            y = self.shared.forward(ctx, x)
+            if isinstance(y, ops.Partials):
+                for s in range(y.nsplit):
+                    ops.add_residual(out, y.t[s, :n])
+            elif y is not None and y is not ops.ADDED:
+                ops.add_residual(out, y[:n])
         return ops.Partials(out.view(1, n, self.hidden))

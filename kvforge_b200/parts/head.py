@@ -12,8 +12,9 @@ from .base import Head, WeightDecl, register_head
 
 @register_head("linear_head")
 class LinearHead(Head):
-    """params: ``vocab_size``, ``hidden_size``; optional ``softcap`` (``c``: the logits become
-    ``c * tanh(logits / c)``).  Its tensor is optional in a checkpoint."""
+    """params: ``vocab_size``, ``hidden_size``; optional ``scale`` (the logits are multiplied by it) and
+    ``softcap`` (``c``: the logits, scaled, become ``c * tanh(logits / c)``).  Its tensor is optional in a
+    checkpoint."""
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -21,6 +22,7 @@ class LinearHead(Head):
         self.hidden = int(params["hidden_size"])
         self.weight = None
         self.softcap = float(params.get("softcap") or 0.0)
+        self.scale = float(params.get("scale") if params.get("scale") is not None else 1.0)
         if self.softcap < 0:
             raise ValueError("softcap must be positive")
 
@@ -43,6 +45,6 @@ class LinearHead(Head):
             ops.gemm_skinny(x, self.weight, logits)
         else:
             ops.linear(x, self.weight, logits)
-        if self.softcap:
-            ops.softcap(logits, self.softcap)
+        if self.scale != 1.0 or self.softcap:
+            ops.scale_softcap(logits, self.scale, self.softcap)
         return logits

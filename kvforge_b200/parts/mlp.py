@@ -58,3 +58,64 @@ class GatedMLP(FeedForward):
             ops.linear(x, self.w_gate_up, gu)
             ops.silu_mul(gu, act, interleaved=self.interleaved)
         return project(rt, "mlp.out", act, self.w_down, ctx)
+
+
+@register_feed_forward("plain_mlp")
+class PlainMLP(FeedForward):
+    """``down(act(up(x)))`` without biases and without a gate.  params: ``hidden_size``, ``intermediate_size``,
+    ``activation``: ``"xielu"`` (with the tensor ``act [2]`` = (p, q): ``z > 0: softplus(p) z^2 + z/2``,
+    ``z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2``), ``"relu2"`` (the square of relu) or ``"gelu_tanh"``.
+    The activation is computed in 32-bit and rounded once.  A block may hand it further rows for its first
+    product (``stack_input``): their result for the step is ``self.extra_out`` after ``forward``."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = params.get("activation", "relu2")
+        if self.activation not in ops.UNARY_ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not one of {sorted(ops.UNARY_ACTIVATIONS)}")
+        self.extra_w = None
+        self.extra_out = None
+
+    @classmethod
+    def weight_decls(cls, params):
+        h, i = int(params["hidden_size"]), int(params["intermediate_size"])
+        out = {"up": WeightDecl((i, h)), "down": WeightDecl((h, i))}
+        if params.get("activation", "relu2") == "xielu":
+            out["act"] = WeightDecl((2,), kind="vector", init="small")
+        return out
+
+    def stack_input(self, w: torch.Tensor) -> bool:
+        self.extra_w = w
+        self._stack()
+        return True
+
+    def _stack(self) -> None:
+        mats = [self._up]
+        self.extra_off = -(-self.inter // 8) * 8
+        if self.extra_w is not None:
+            if self.extra_off > self.inter:
+                mats.append(torch.zeros((self.extra_off - self.inter, self.hidden), dtype=self._up.dtype, device=self._up.device))
+            mats.append(self.extra_w)
+        self.w_up = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else self._up.contiguous()
+
+    def bind(self, weights, rt):
+        super().bind(weights, rt)
+        self._up = weights["up"]
+        self._stack()
+        self.w_down = weights["down"].contiguous()
+        self.ab = weights["act"].contiguous() if self.activation == "xielu" else None
+
+    def forward(self, ctx, x: torch.Tensor):
+        rt = self.rt
+        n = x.shape[0]
+        u = rt.buf("pmlp.up", n, self.w_up.shape[0])
+        if ops.skinny_ok(x, self.w_up):
+            ops.gemm_skinny(x, self.w_up, u)
+        else:
+            ops.linear(x, self.w_up, u)
+        self.extra_out = u[:, self.extra_off : self.extra_off + self.extra_w.shape[0]] if self.extra_w is not None else None
+        act = rt.buf("pmlp.act", n, self.inter)
+        ops.unary_act(u[:, : self.inter], act, self.activation, self.ab)
+        return project(rt, "pmlp.out", act, self.w_down, ctx)

@@ -33,6 +33,9 @@ class LayerCall:
     # row of the model's ``pass_offsets`` tensor that is added to every token of the residual stream right
     # before this call (a stretch of layers that runs several times marks each pass so)
     offset_row: int | None = None
+    # right before this call the stream becomes ``W_in [x; x0]``: ``x`` the stream as it stands, ``x0`` the
+    # embedding's output, ``W_in`` the model's ``pass_mix`` tensor ``[hidden, 2 * hidden]``
+    mix_input: bool = False
 
 
 @dataclass
@@ -67,6 +70,11 @@ class ModelSpec:
     # float tensor ``[rows, hidden]`` whose rows the calls' ``offset_row`` name, and its checkpoint name
     pass_offsets: int = 0
     pass_offsets_name: str = "loop.step"
+    # a norm applied to the embedding's output before anything else reads it (the normed rows are the stream)
+    embedding_norm: PartSpec | None = None
+    embedding_norm_prefix: str = "embed."
+    # checkpoint name of the matrix ``[hidden, 2 * hidden]`` that calls with ``mix_input`` apply to ``[x; x0]``
+    pass_mix_name: str | None = None
 
     def __post_init__(self) -> None:
         if not self.execution:
@@ -76,6 +84,8 @@ class ModelSpec:
                 raise ValueError(f"execution[{idx}] names layer {call.layer}, which does not exist")
             if call.offset_row is not None and not 0 <= call.offset_row < self.pass_offsets:
                 raise ValueError(f"execution[{idx}].offset_row names a row that pass_offsets does not have")
+            if call.mix_input and not self.pass_mix_name:
+                raise ValueError(f"execution[{idx}].mix_input needs the model's pass_mix_name")
             if call.kv_from is not None:
                 if not 0 <= call.kv_from < idx:
                     raise ValueError(f"execution[{idx}].kv_from must name an earlier call")
@@ -112,6 +122,8 @@ class DecoderModel:
         if spec.residual_streams < 1:
             raise ValueError("residual_streams must be at least 1")
         self.input_position = build_part("position", spec.input_position, spec.input_position_prefix) if spec.input_position else None
+        self.embedding_norm = build_part("norm", spec.embedding_norm, spec.embedding_norm_prefix) if spec.embedding_norm else None
+        self.mixes_input = any(call.mix_input for call in spec.execution)
         # cache groups from what the mixers declare
         self.groups: list[CacheGroup] = []
         self.call_group: list[tuple[int, int] | None] = []  # per call: (group, entry) of its own cache
@@ -151,6 +163,8 @@ class DecoderModel:
                 out[part.tensor_name(local)] = decl
         if self.spec.pass_offsets:
             out[self.spec.pass_offsets_name] = WeightDecl((self.spec.pass_offsets, self.spec.hidden_size), kind="vector", init="zeros")
+        if self.mixes_input:
+            out[self.spec.pass_mix_name] = WeightDecl((self.spec.hidden_size, 2 * self.spec.hidden_size), init="mix_in")
         return out
 
     def _all_parts(self):
@@ -169,6 +183,8 @@ class DecoderModel:
         yield self.final_norm
         if self.input_position is not None:
             yield self.input_position
+        if self.embedding_norm is not None:
+            yield self.embedding_norm
 
     def bind(self, weights: dict[str, torch.Tensor], rt) -> None:
         s = self.spec
@@ -190,6 +206,11 @@ class DecoderModel:
         self.pass_offsets = weights[s.pass_offsets_name] if s.pass_offsets else None
         if s.pass_offsets and s.residual_streams != 1:
             raise ValueError("rows added between passes need a single residual stream")
+        self.pass_mix = weights[s.pass_mix_name].contiguous() if self.mixes_input else None
+        if (self.mixes_input or self.embedding_norm is not None) and s.residual_streams != 1:
+            raise ValueError("a normed embedding and a stream mixed with it need a single residual stream")
+        if self.mixes_input and not hasattr(self.final_norm, "settle"):
+            raise ValueError("a stream mixed with the embedding's output needs a norm that can settle what is pending")
         if s.tie_word_embeddings or self.head.tensor_name("weight") not in weights:
             self.head.tie(self.embedding.table())
 
@@ -208,6 +229,15 @@ class DecoderModel:
         ctx.residual = resid
         if self.input_position is not None:
             self.input_position.embed(ctx, resid)
+        width = self.spec.hidden_size
+        both = None
+        if self.mixes_input:
+            # [x; x0] side by side in the storage type: x0, the embedding's output, is written once a step
+            both = rt.buf("model.mix_in", ctx.num_tokens, 2 * width)
+        if self.embedding_norm is not None:
+            self.embedding_norm.replace(ctx, resid, both[:, width:] if both is not None else None)
+        elif both is not None:
+            self.final_norm.settle(ctx, resid, None, both[:, width:])
         if self.spec.residual_streams > 1:
             # every stream starts as the embedding's output; no part may add into a single stream
             streams = rt.buf("model.streams", ctx.num_tokens, self.spec.residual_streams * self.spec.hidden_size, torch.float32)
@@ -219,6 +249,14 @@ class DecoderModel:
                 # the sum still pending from the layer before is added by this layer's norm: the order of the two
                 # additions does not matter beyond rounding
                 ops.add_row(resid, self.pass_offsets[call.offset_row])
+            if call.mix_input:
+                # what is pending joins the stream, the stream goes beside x0, and their product is the new stream
+                self.final_norm.settle(ctx, resid, delta, both[:, :width])
+                delta = None
+                if ops.skinny_ok(both, self.pass_mix):
+                    ops.gemm_skinny(both, self.pass_mix, resid)
+                else:
+                    ops.linear(both, self.pass_mix, resid)
             delta = self.blocks[call.layer].forward(ctx, resid, delta, self.caches[idx])
         return resid, delta
 

@@ -68,3 +68,39 @@ class StreamRMSNorm(Norm):
         out = self.rt.buf("norm.out" if rows is None else "norm.rows", n, self.dim)
         ops.stream_step(resid, delta, read, self.weight, out, self.eps, self.streams, rows)
         return out
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """Layer norm with a weight and no bias, ``(x - mean) / sqrt(var + eps) * w`` with the variance of the
+    deviations, in 32-bit.  params: ``dim``, ``eps``; optional ``centred`` (default true; false: the RMS norm
+    through the same kernel).  What the sublayer before left pending may be an ``ops.GatedWrite``: a result that
+    is gated, normed in the same way with a weight of its own and only then added to the stream."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.dim = int(params["dim"])
+        self.eps = float(params["eps"])
+        self.centred = bool(params.get("centred", True))
+
+    @classmethod
+    def weight_decls(cls, params):
+        return {"weight": WeightDecl((int(params["dim"]),), kind="vector", init="ones")}
+
+    def bind(self, weights, rt):
+        super().bind(weights, rt)
+        self.weight = weights["weight"]
+
+    def forward(self, ctx, resid: torch.Tensor, delta, rows: torch.Tensor | None = None, num_rows: int | None = None):
+        n = num_rows if rows is not None else resid.shape[0]
+        out = self.rt.buf("norm.out" if rows is None else "norm.rows", n, self.dim)
+        ops.norm_step(resid, delta, self.weight, out, self.eps, self.centred, rows)
+        return out
+
+    def settle(self, ctx, resid: torch.Tensor, delta, out: torch.Tensor | None = None) -> None:
+        """Adds what is pending into the stream without norming it; ``out`` (storage type) gets the stream's rows."""
+        ops.norm_step(resid, delta, None, out, self.eps, self.centred)
+
+    def replace(self, ctx, resid: torch.Tensor, out: torch.Tensor | None = None) -> None:
+        """The stream itself becomes its normed rows (float); ``out`` gets them in the storage type."""
+        ops.norm_step(resid, None, self.weight, out, self.eps, self.centred, store_normed=True)

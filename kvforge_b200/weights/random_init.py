@@ -50,6 +50,10 @@ def draw(name: str, decl: WeightDecl, seed: int, device: torch.device | str = "c
         return 0.5 * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
     if decl.init == "small":  # logarithms of rates and biases of step sizes: of order one
         return 0.5 * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
+    if decl.init == "mix_in":  # [W, 2W] applied to [x; x0]: x passes, a little of x0 comes in
+        w = decl.shape[0]
+        t = torch.cat([torch.eye(w, dtype=torch.float32, device=device), torch.zeros((w, decl.shape[1] - w), dtype=torch.float32, device=device)], dim=1)
+        return t + init_std * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
     if decl.init == "wide":  # the second matrix of a low-rank pair: its input is small already
         return (decl.shape[-1] ** -0.5) * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
     return init_std * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
