@@ -600,11 +600,12 @@ def run_load(cfg, nreq: int, short_prompts: bool = False) -> dict:
             "tpot_p50_ms": round(m["tpot_p50_ms"], 3), "preemptions": stats["scheduler"]["num_preemptions"]}  # fmt: skip
 
 
-DESIGN_PAIRS = (("mopilorn-1b", "llama-3.2-1b"), ("mopilorn-3b", "llama-3.2-3b"), ("setenex-1b", "llama-3.2-1b"))
+DESIGN_PAIRS = (("mopilorn-1b", "llama-3.2-1b"), ("mopilorn-3b", "llama-3.2-3b"), ("setenex-1b", "llama-3.2-1b"), ("gukirax-1b", "llama-3.2-1b"),
+                ("gukirax-3b", "llama-3.2-3b"))  # fmt: skip
 
 
 def run_designs(args) -> dict:
-    """Prompt and decode throughput of the Mopilorn and Setenex shapes beside the Llama shapes of equal width,
+    """Prompt and decode throughput of the Mopilorn, Setenex and Gukirax shapes beside the Llama shapes of equal width,
     depth, feed-forward per token and vocabulary (random weights): a prompt of 2,048 tokens, and decode steps of 8
     and 64 requests with 2,048 tokens behind them, each as captured graphs, timed on the device.  ``--design NAME``
     runs the one pair that holds the named shape."""
@@ -855,7 +856,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "attention", "attention-prefill", "gemm", "sample", "load", "designs"], help="run one part alone and print a short line (for profiling); 'designs': the Mopilorn and Setenex shapes beside the Llama shapes of equal size")
+    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "attention", "attention-prefill", "gemm", "sample", "load", "designs"], help="run one part alone and print a short line (for profiling); 'designs': the Mopilorn, Setenex and Gukirax shapes beside the Llama shapes of equal size")
     ap.add_argument("--design", default=None, help="with --only designs: the one pair that holds this named shape (default: all pairs)")
     ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b, mopilorn-1b, mopilorn-3b)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")

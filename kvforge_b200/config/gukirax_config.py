@@ -186,7 +186,8 @@ def uniform(
 
 # Named shapes with random weights: a small one for demonstrations, and one with the width, depth, heads and
 # vocabulary of the 1B Llama shape this engine is measured on (a token's feed-forward flops are that shape's:
-# 4 of 32 experts of 1,536 and a shared expert of 2,048; the first layer is dense).
+# 4 of 32 experts of 1,536 and a shared expert of 2,048; the first layer is dense), and one with those of the 3B
+# Llama shape, heads of 128, and a stretch of four layers that runs twice.
 GUKIRAX_PRESETS: dict[str, GukiraxConfig] = {
     "gukirax-tiny": uniform(
         vocab=256, width=96, num_layers=3, heads=4, kv_heads=2, dim=32, rot_dims=16, dense_ff=160, dense_layers=1, experts=8, top=2, ff=48,
@@ -195,5 +196,9 @@ GUKIRAX_PRESETS: dict[str, GukiraxConfig] = {
     "gukirax-1b": uniform(
         vocab=128256, width=2048, num_layers=16, heads=32, kv_heads=8, dim=64, rot_dims=32, dense_ff=8192, dense_layers=1, experts=32, top=4,
         ff=1536, shared_ff=2048, base=500000.0, logit_scale=0.125,
+    ),
+    "gukirax-3b": uniform(
+        vocab=128256, width=3072, num_layers=24, heads=24, kv_heads=8, dim=128, rot_dims=64, dense_ff=8192, dense_layers=2, experts=32, top=4,
+        ff=1536, shared_ff=2048, loop=LoopConfig(10, 14, 2), base=500000.0, logit_scale=0.125,
     ),
 }  # fmt: skip

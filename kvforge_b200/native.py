@@ -44,7 +44,7 @@ LIBRARIES: dict[str, tuple[list[str], list[str]]] = {
     "routed": (["head_ops.cu", "experts.cu"], []),
     # layers whose sublayer results are gated and normed before they join the residual stream, heads that are
     # rotated and then normed, attention whose heads talk before the softmax; a library of its own for the same reason
-    "gated": (["gated_ops.cu", "attention_talking_f32.cu", "attention_talking_bf16.cu"], []),
+    "gated": (["gated_ops.cu", "attention_talking_f32.cu", "attention_talking_bf16.cu", "attention_talking_mma.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -67,6 +67,8 @@ _SIGNATURES = {
     "kvf_qk_prepare_{s}": "pliiippiifpppiiiiiilpp",
     "kvf_unary_act_{s}": "plplliipp",
     "kvf_talking_attention_{s}": "pppppppppiiiiiiiiiifiiiippp",
+    "kvf_talking_attention_mma_bf16": "pppppppppiiiiiiiiiifiiiippp",
+    "kvf_talking_mma_ok": "iiiiii",
     "kvf_gated_set_pdl": "i",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
@@ -1763,6 +1765,20 @@ def scale_softcap(logits: torch.Tensor, scale: float, cap: float) -> None:
 
 
 TALKING_MAX_HEADS = 64  # what the kernel's CTA of eight warps holds: a row per (head, query), eight rows a warp
+TALKING_MMA_RANGE_STEP = 32  # keys per tile of the tensor-core form's key ranges
+
+_talking_mma_known: dict[tuple, bool] = {}
+
+
+def talking_mma_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, dv: int, decode_form: bool, talk: bool = True) -> bool:
+    """Whether the tensor-core form of ``talking_attention`` takes this shape: bfloat16 storage, heads of 64 or 128
+    with values as wide as keys, and head counts whose rows and tiles fit a CTA (the library decides)."""
+    if dtype != torch.bfloat16 or d != dv or d not in (64, 128):
+        return False
+    key = (nh, nkv, d, bool(decode_form), bool(talk))
+    if key not in _talking_mma_known:
+        _talking_mma_known[key] = bool(_fn("kvf_talking_mma_ok", GATED_LIB)(nh, nkv, d, dv, 1 if decode_form else 0, 1 if talk else 0))
+    return _talking_mma_known[key]
 
 
 def talking_attention(
@@ -1805,6 +1821,8 @@ def talking_attention(
         if acc.shape[0] < num_seqs or acc.shape[1] != nh or acc.shape[3] != dv or -(-bound // split) > max_splits:
             raise ValueError("talking_attention: scratch too small for this step")
     name = f"kvf_talking_attention_{s}"
+    if talking_mma_supported(q.dtype, nh, nkv, d, dv, scratch is not None, talk is not None) and (scratch is None or split % TALKING_MMA_RANGE_STEP == 0):
+        name = "kvf_talking_attention_mma_bf16"  # the two products on the tensor cores; mixing, softmax and sink in float
     _check(
         _fn(name, GATED_LIB)(
             _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(query_start_loc), _ptr(context_lens), _ptr(talk), _ptr(sink),
