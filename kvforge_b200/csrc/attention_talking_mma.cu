@@ -84,19 +84,49 @@ template <int D> __device__ __forceinline__ uint32_t tile_off(int row, int chunk
   return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
 }
 
-// Keys [t0, t0 + BN) of every kv head into one swizzled tile a head.  Keys at or past `ctx` and keys in pages
-// that were given back are zeros.
+// Where the keys [t0, t0 + BN) lie: koff[key] = (page * nkv * block_size + place in the page) in keys, or -1 for a
+// key at or past `ctx` or in a page that was given back.  Written by the first BN threads.
+template <int BN>
+__device__ __forceinline__ void locate_keys(const int* bt, int t0, int ctx, int nkv, int block_size, int* koff) {
+  if (threadIdx.x < BN) {
+    const int kp = t0 + threadIdx.x;
+    int off = -1;
+    if (kp < ctx) {
+      const int pg = kp / block_size;
+      const int blk = bt[pg];
+      if (blk >= 0) off = blk * nkv * block_size + (kp - pg * block_size);
+    }
+    koff[threadIdx.x] = off;
+  }
+}
+
+// The keys that `koff` locates, of every kv head, into one swizzled tile a head; keys that are not there are zeros.
 template <int D, int BN>
-__device__ __forceinline__ void load_tiles(const bf16* cache, const int* bt, int t0, int ctx, int nkv, int block_size, uint32_t dst) {
+__device__ __forceinline__ void load_tiles(const bf16* cache, const int* koff, int nkv, int block_size, uint32_t dst) {
   constexpr int CH = D / 8;
-  for (int idx = threadIdx.x; idx < nkv * BN * CH; idx += NW * 32) {
-    const int c = idx / (BN * CH), rem = idx - c * (BN * CH);
-    const int key = rem / CH, chunk = rem - key * CH;
-    const int kp = t0 + key;
-    const int blk = kp < ctx ? bt[kp / block_size] : -1;
-    const bool valid = blk >= 0;
-    const size_t base = valid ? (((size_t)blk * nkv + c) * block_size + (kp % block_size)) * D + chunk * 8 : 0;
-    cp_async16(dst + (uint32_t)c * (BN * D * 2) + tile_off<D>(key, chunk), cache + base, valid);
+  const int chunk = threadIdx.x % CH;
+  const int key0 = threadIdx.x / CH;
+  constexpr int KSTEP = NW * 32 / CH;  // keys between a thread's chunks of one head
+  static_assert(BN % KSTEP == 0 || KSTEP % BN == 0, "tile and CTA sizes");
+  if (KSTEP <= BN) {
+    for (int c = 0; c < nkv; ++c) {
+#pragma unroll
+      for (int key = key0; key < BN; key += KSTEP) {
+        const int off = koff[key];
+        const bool valid = off >= 0;
+        const size_t base = valid ? ((size_t)off + (size_t)c * block_size) * D + chunk * 8 : 0;
+        cp_async16(dst + (uint32_t)c * (BN * D * 2) + tile_off<D>(key, chunk), cache + base, valid);
+      }
+    }
+  } else {  // a pass of the CTA covers several heads
+    constexpr int HEADS = KSTEP / BN;
+    const int key = key0 % BN, c0 = key0 / BN;
+    const int off = koff[key];
+    const bool valid = off >= 0;
+    for (int c = c0; c < nkv; c += HEADS) {
+      const size_t base = valid ? ((size_t)off + (size_t)c * block_size) * D + chunk * 8 : 0;
+      cp_async16(dst + (uint32_t)c * (BN * D * 2) + tile_off<D>(key, chunk), cache + base, valid);
+    }
   }
 }
 
@@ -164,6 +194,7 @@ __global__ void __launch_bounds__(NW * 32) talking_mma_kernel(const Params p) {
   float* Ss = reinterpret_cast<float*>(Vb + (size_t)nkv * BN * D * 2);  // [nh][tq][BNP]
   float* Ps = p.talk ? Ss + (size_t)nh * per_h : Ss;
   float* Tt = Ps + (size_t)nh * per_h;                            // [nh][nhp]: Tt[g][h] = talk[h][g]
+  int* koff = reinterpret_cast<int*>(Tt + (p.talk ? (size_t)nh * nhp : 0));  // [2][BN]: where a tile's keys lie
   const uint32_t kb = smem_u32(Kb), vb = smem_u32(Vb);
 
   const int b = blockIdx.y;
@@ -180,7 +211,7 @@ __global__ void __launch_bounds__(NW * 32) talking_mma_kernel(const Params p) {
     if (kv_lo >= ctx) return;  // a range past the context: the merge never reads it
     kv_hi = min(ctx, kv_lo + p.split_size);
   } else {
-    q0 = blockIdx.x * tq;
+    q0 = (gridDim.x - 1 - blockIdx.x) * tq;  // the queries with the most keys first
     if (q0 >= q_len) return;
     n_tok = min(tq, q_len - q0);
     kv_lo = 0;
@@ -188,14 +219,15 @@ __global__ void __launch_bounds__(NW * 32) talking_mma_kernel(const Params p) {
   }
   const int* bt = p.block_tables + (size_t)b * p.bt_stride;
 
-  load_tiles<D, BN>(p.kcache, bt, kv_lo, ctx, nkv, p.block_size, kb);
-  cp_async_commit();
-
+  locate_keys<BN>(bt, kv_lo, ctx, nkv, p.block_size, koff);
   if (p.talk)
     for (int idx = threadIdx.x; idx < nh * nhp; idx += NW * 32) {
       const int g = idx / nhp, h = idx - g * nhp;
       Tt[idx] = h < nh ? p.talk[(size_t)h * nh + g] : 0.f;
     }
+  __syncthreads();
+  load_tiles<D, BN>(p.kcache, koff, nkv, p.block_size, kb);
+  cp_async_commit();
 
   // ---- the rows this warp owns: m-tile mt = warp + k * NW of kv head mt / mtc; a thread holds rows lane/4 and lane/4 + 8
   const int n_mt = nkv * p.mtc;
@@ -235,11 +267,14 @@ __global__ void __launch_bounds__(NW * 32) talking_mma_kernel(const Params p) {
   }
   const float scale2 = p.scale * LOG2E;  // scores in units of log 2: the mixing is linear, so the factor may come first
 
-  for (int t0 = kv_lo; t0 < kv_hi; t0 += BN) {
+  int cur = 0;
+  for (int t0 = kv_lo; t0 < kv_hi; t0 += BN, cur ^= 1) {
     cp_async_wait<0>();
     __syncthreads();  // the key tiles have landed; the value tiles and score tiles of the tile before are consumed
-    load_tiles<D, BN>(p.vcache, bt, t0, ctx, nkv, p.block_size, vb);
+    load_tiles<D, BN>(p.vcache, koff + cur * BN, nkv, p.block_size, vb);
     cp_async_commit();
+    const bool more = t0 + BN < kv_hi;
+    if (more) locate_keys<BN>(bt, t0 + BN, ctx, nkv, p.block_size, koff + (cur ^ 1) * BN);
     // ---- 1. scores
 #pragma unroll
     for (int k = 0; k < MT; ++k) {
@@ -272,9 +307,8 @@ __global__ void __launch_bounds__(NW * 32) talking_mma_kernel(const Params p) {
       }
     }
     __syncthreads();  // every head's scores are written; the key tiles are consumed
-    const bool more = t0 + BN < kv_hi;
     if (more) {
-      load_tiles<D, BN>(p.kcache, bt, t0 + BN, ctx, nkv, p.block_size, kb);
+      load_tiles<D, BN>(p.kcache, koff + (cur ^ 1) * BN, nkv, p.block_size, kb);
       cp_async_commit();
     }
     // ---- 2. the heads talk
@@ -396,7 +430,7 @@ struct Plan {
 
 inline size_t smem_need(int nh, int nkv, int d, int tq, int bn, bool talk) {
   const int nhp = (nh + HC - 1) / HC * HC;
-  return (size_t)2 * nkv * bn * d * 2 + (size_t)(talk ? 2 : 1) * nh * tq * (bn + 8) * 4 + (talk ? (size_t)nh * nhp * 4 : 0);
+  return (size_t)2 * nkv * bn * d * 2 + (size_t)(talk ? 2 : 1) * nh * tq * (bn + 8) * 4 + (talk ? (size_t)nh * nhp * 4 : 0) + (size_t)2 * bn * 4;
 }
 
 // The most queries a CTA that fit: every m-tile has a warp (two a warp for heads of 64), everything in shared memory.

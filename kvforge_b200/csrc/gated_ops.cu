@@ -104,6 +104,149 @@ __global__ void __launch_bounds__(256) norm_step_kernel(const NormStepParams p) 
   }
 }
 
+// The same pass for rows of up to 4 * 256 * NIT numbers whose rows start on 16-byte boundaries: a thread owns
+// four neighbouring numbers of each of up to NIT quarters of the row and keeps them in registers; everything a
+// row needs from memory is asked for before the first number is used.  The sums run in the same order whatever
+// else is in the batch.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* src, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(src);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float* dst, const float* f) {
+    *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+template <> struct Vec4<bf16> {
+  static __device__ __forceinline__ void load(const bf16* src, float* f) {
+    const uint2 u = *reinterpret_cast<const uint2*>(src);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    f[0] = __low2float(a); f[1] = __high2float(a); f[2] = __low2float(b); f[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(bf16* dst, const float* f) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&a);
+    u.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(dst) = u;
+  }
+};
+
+template <int NIT>
+__device__ __forceinline__ void reg_stats(const float (&x)[NIT][4], const bool (&live)[NIT], int W, int centred, float eps,
+                                          float* red, float& mean, float& rstd) {
+  mean = 0.f;
+  if (centred) {
+    float s = 0.f;
+#pragma unroll
+    for (int it = 0; it < NIT; ++it)
+      if (live[it]) s += (x[it][0] + x[it][1]) + (x[it][2] + x[it][3]);
+    mean = block_sum(s, red) / (float)W;
+  }
+  float q = 0.f;
+#pragma unroll
+  for (int it = 0; it < NIT; ++it)
+    if (live[it]) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float d = x[it][e] - mean;
+        q = fmaf(d, d, q);
+      }
+    }
+  rstd = 1.f / sqrtf(block_sum(q, red) / (float)W + eps);
+}
+
+template <typename T, int NIT>
+__global__ void __launch_bounds__(256) norm_step_vec_kernel(const NormStepParams p) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float red[32];
+  const int W = p.W;
+  const int r = blockIdx.x;
+  const int src = p.rows ? p.rows[r] : r;
+  float* h = p.resid + (size_t)src * W;
+  const bool pending = p.y != nullptr || p.y_parts != nullptr;
+  const T* y = p.y ? (const T*)p.y + (size_t)src * p.y_stride : nullptr;
+  const float* yp = p.y_parts ? p.y_parts + (size_t)src * W : nullptr;
+  const T* z = (pending && p.z) ? (const T*)p.z + (size_t)src * p.z_stride : nullptr;
+  bool live[NIT];
+  float hv[NIT][4], a[NIT][4], g[NIT][4], pw[NIT][4], nw[NIT][4];
+#pragma unroll
+  for (int it = 0; it < NIT; ++it) {
+    const int i = (it * 256 + threadIdx.x) * 4;
+    live[it] = i < W;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) hv[it][e] = a[it][e] = g[it][e] = 0.f, pw[it][e] = nw[it][e] = 1.f;
+    if (!live[it]) continue;
+    Vec4<float>::load(h + i, hv[it]);
+    if (p.next_w) Vec4<float>::load(p.next_w + i, nw[it]);
+    if (!pending) continue;
+    if (y) Vec4<T>::load(y + i, a[it]);
+    if (z) {
+      Vec4<T>::load(z + i, g[it]);
+      if (p.z_bias) {
+        float zb[4];
+        Vec4<float>::load(p.z_bias + i, zb);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) g[it][e] += zb[e];
+      }
+    }
+    if (p.post_w) Vec4<float>::load(p.post_w + i, pw[it]);
+  }
+  if (yp) {
+    for (int s = 0; s < p.nsplit; ++s) {
+#pragma unroll
+      for (int it = 0; it < NIT; ++it) {
+        if (!live[it]) continue;
+        float t[4];
+        Vec4<float>::load(yp + (size_t)s * p.split_stride + (it * 256 + threadIdx.x) * 4, t);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a[it][e] += t[e];
+      }
+    }
+  }
+  if (pending) {
+    if (z) {
+#pragma unroll
+      for (int it = 0; it < NIT; ++it)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a[it][e] *= 1.f / (1.f + expf(-g[it][e]));
+    }
+    float mean = 0.f, rstd = 1.f;
+    if (p.post_w) reg_stats<NIT>(a, live, W, p.centred, p.eps, red, mean, rstd);
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) hv[it][e] += p.post_w ? (a[it][e] - mean) * rstd * pw[it][e] : a[it][e];
+      if (live[it] && !p.rows && !p.store_normed) Vec4<float>::store(h + (it * 256 + threadIdx.x) * 4, hv[it]);
+    }
+  }
+  if (!p.out && !p.store_normed) return;
+  float mean = 0.f, rstd = 1.f;
+  if (p.next_w) reg_stats<NIT>(hv, live, W, p.centred, p.eps, red, mean, rstd);
+  T* o = p.out ? (T*)p.out + (size_t)r * p.out_stride : nullptr;
+#pragma unroll
+  for (int it = 0; it < NIT; ++it) {
+    if (!live[it]) continue;
+    const int i = (it * 256 + threadIdx.x) * 4;
+    float x[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x[e] = p.next_w ? (hv[it][e] - mean) * rstd * nw[it][e] : hv[it][e];
+    if (o) Vec4<T>::store(o + i, x);
+    if (p.store_normed && !p.rows) Vec4<float>::store(h + i, x);
+  }
+}
+
+template <typename T>
+bool norm_step_vec_ok(const NormStepParams& p) {
+  auto al = [](const void* q, size_t n) { return q == nullptr || ((uintptr_t)q % n) == 0; };
+  constexpr size_t TB = 4 * sizeof(T);
+  return p.W % 4 == 0 && p.W <= 4 * 256 * 4 && al(p.resid, 16) && al(p.y_parts, 16) && al(p.z_bias, 16) && al(p.post_w, 16) &&
+         al(p.next_w, 16) && al(p.y, TB) && al(p.z, TB) && al(p.out, TB) && p.y_stride % 4 == 0 && p.z_stride % 4 == 0 &&
+         p.out_stride % 4 == 0 && p.split_stride % 4 == 0;
+}
+
 // ---------------------------------------------------------------- rotation, head norm, cache write
 // A row of `x` holds nh query heads of d numbers from column 0, nkv key heads of d from column k_off, and the
 // value heads' sources from column v_off (v_step numbers apart, the first dv of each are the value; with
@@ -242,6 +385,11 @@ KVF_API int kvf_gated_set_pdl(int enabled) {
     p.resid = resid; p.rows = rows; p.y = y; p.y_parts = y_parts; p.y_stride = y_stride; p.split_stride = split_stride; \
     p.nsplit = nsplit; p.z = z; p.z_stride = z_stride; p.z_bias = z_bias; p.post_w = post_w; p.next_w = next_w;       \
     p.out = out; p.out_stride = out_stride; p.W = W; p.centred = centred; p.store_normed = store_normed; p.eps = eps; \
+    if (norm_step_vec_ok<T>(p)) {                                                                                     \
+      if (W <= 1024) return launch(norm_step_vec_kernel<T, 1>, dim3(n_rows), dim3(256), 0, st, p);                    \
+      if (W <= 2048) return launch(norm_step_vec_kernel<T, 2>, dim3(n_rows), dim3(256), 0, st, p);                    \
+      return launch(norm_step_vec_kernel<T, 4>, dim3(n_rows), dim3(256), 0, st, p);                                   \
+    }                                                                                                                 \
     const size_t smem = (size_t)2 * W * sizeof(float);                                                                \
     auto kern = norm_step_kernel<T>;                                                                                  \
     if (smem > 48 * 1024) {                                                                                           \
