@@ -27,6 +27,7 @@ namespace tmma {
 constexpr int HC = 8;           // target heads a warp mixes at a time
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr size_t SMEM_MOST = 220 * 1024;
+constexpr size_t TWO_CTAS = 112 * 1024;  // what a CTA may hold for two to share an SM
 
 struct Params {
   const bf16* q;
@@ -144,27 +145,25 @@ __device__ __forceinline__ void mix_heads(const float* Ss, float* Ps, const floa
       const int col = (grp * C + k) * 32 + lane;
       off[k] = (col / BN) * BNP + (col % BN);
     }
-    float acc[C][HC];
+    float2 acc[C][HC / 2];  // pairs of neighbouring target heads: one packed FMA moves both
 #pragma unroll
     for (int k = 0; k < C; ++k)
 #pragma unroll
-      for (int e = 0; e < HC; ++e) acc[k][e] = 0.f;
+      for (int e = 0; e < HC / 2; ++e) acc[k][e] = make_float2(0.f, 0.f);
     const float* trow = Tt + chunk * HC;
     for (int g = 0; g < nh; ++g) {
       const float4 ta = *reinterpret_cast<const float4*>(trow + g * nhp);
       const float4 tb = *reinterpret_cast<const float4*>(trow + g * nhp + 4);
+      const float2 t0 = make_float2(ta.x, ta.y), t1 = make_float2(ta.z, ta.w), t2 = make_float2(tb.x, tb.y), t3 = make_float2(tb.z, tb.w);
       const float* srow = Ss + g * per_h;
 #pragma unroll
       for (int k = 0; k < C; ++k) {
         const float s = srow[off[k]];
-        acc[k][0] = fmaf(ta.x, s, acc[k][0]);
-        acc[k][1] = fmaf(ta.y, s, acc[k][1]);
-        acc[k][2] = fmaf(ta.z, s, acc[k][2]);
-        acc[k][3] = fmaf(ta.w, s, acc[k][3]);
-        acc[k][4] = fmaf(tb.x, s, acc[k][4]);
-        acc[k][5] = fmaf(tb.y, s, acc[k][5]);
-        acc[k][6] = fmaf(tb.z, s, acc[k][6]);
-        acc[k][7] = fmaf(tb.w, s, acc[k][7]);
+        const float2 s2 = make_float2(s, s);
+        acc[k][0] = __ffma2_rn(t0, s2, acc[k][0]);
+        acc[k][1] = __ffma2_rn(t1, s2, acc[k][1]);
+        acc[k][2] = __ffma2_rn(t2, s2, acc[k][2]);
+        acc[k][3] = __ffma2_rn(t3, s2, acc[k][3]);
       }
     }
 #pragma unroll
@@ -172,14 +171,14 @@ __device__ __forceinline__ void mix_heads(const float* Ss, float* Ps, const floa
       const int h = chunk * HC + e;
       if (h < nh) {
 #pragma unroll
-        for (int k = 0; k < C; ++k) Ps[h * per_h + off[k]] = acc[k][e];
+        for (int k = 0; k < C; ++k) Ps[h * per_h + off[k]] = (e & 1) ? acc[k][e / 2].y : acc[k][e / 2].x;
       }
     }
   }
 }
 
 template <int D, int BN, int MT, bool SPLIT>
-__global__ void __launch_bounds__(NW * 32) talking_mma_kernel(const Params p) {
+__global__ void __launch_bounds__(NW * 32, (D == 64 && BN == 32 && MT == 1) ? 2 : 1) talking_mma_kernel(const Params p) {
   pdl_launch();
   pdl_wait();
   constexpr int BNP = BN + 8;  // row stride of the score tiles: rows eight apart fall into other banks
@@ -333,18 +332,28 @@ __global__ void __launch_bounds__(NW * 32) talking_mma_kernel(const Params p) {
         const float* src = Ps + (srow[k][rr] < 0 ? 0 : srow[k][rr]) + (lane & 3) * 2;
         const int ps = pos[k][rr];
         float mx = -INFINITY;
+        if (ps >= t0 + BN - 1 && t0 + BN <= kv_hi && p.window <= 0) {  // the row sees the whole tile
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-          const float2 v = ps >= 0 ? *reinterpret_cast<const float2*>(src + j * 8) : make_float2(0.f, 0.f);
-          const int key = t0 + j * 8 + (lane & 3) * 2;
-          bool v0 = key <= ps && key < kv_hi, v1 = key + 1 <= ps && key + 1 < kv_hi;
-          if (p.window > 0) {
-            v0 = v0 && key > ps - p.window;
-            v1 = v1 && key + 1 > ps - p.window;
+          for (int j = 0; j < NT; ++j) {
+            const float2 v = *reinterpret_cast<const float2*>(src + j * 8);
+            pr[j][2 * rr] = v.x;
+            pr[j][2 * rr + 1] = v.y;
+            mx = fmaxf(mx, fmaxf(v.x, v.y));
           }
-          pr[j][2 * rr] = v0 ? v.x : -INFINITY;
-          pr[j][2 * rr + 1] = v1 ? v.y : -INFINITY;
-          mx = fmaxf(mx, fmaxf(pr[j][2 * rr], pr[j][2 * rr + 1]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            const float2 v = ps >= 0 ? *reinterpret_cast<const float2*>(src + j * 8) : make_float2(0.f, 0.f);
+            const int key = t0 + j * 8 + (lane & 3) * 2;
+            bool v0 = key <= ps && key < kv_hi, v1 = key + 1 <= ps && key + 1 < kv_hi;
+            if (p.window > 0) {
+              v0 = v0 && key > ps - p.window;
+              v1 = v1 && key + 1 > ps - p.window;
+            }
+            pr[j][2 * rr] = v0 ? v.x : -INFINITY;
+            pr[j][2 * rr + 1] = v1 ? v.y : -INFINITY;
+            mx = fmaxf(mx, fmaxf(pr[j][2 * rr], pr[j][2 * rr + 1]));
+          }
         }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -438,7 +447,7 @@ inline bool make_plan(int nh, int nkv, int d, int dv, bool split, int max_q_len,
   if (d != dv || (d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || nh > NW * MAXR) return false;
   const int gs = nh / nkv;
   const int mt_most = d == 64 ? 2 : 1;
-  const int bn = (d == 64 && !split) ? 64 : 32;
+  int bn = (d == 64 && !split) ? 64 : 32;
   int tq_first = split ? 1 : 16;
   while (tq_first > 1 && tq_first / 2 >= max_q_len) tq_first /= 2;
   for (int tq = tq_first; tq >= 1; tq /= 2) {
@@ -448,6 +457,11 @@ inline bool make_plan(int nh, int nkv, int d, int dv, bool split, int max_q_len,
     const size_t need = smem_need(nh, nkv, d, tq, bn, talk);
     if (need > SMEM_MOST) continue;
     pl.tq = tq; pl.mtc = mtc; pl.bn = bn; pl.mt = (n_mt + NW - 1) / NW; pl.smem = need;
+    // heads of 64, one m-tile a warp: with tiles of 32 keys two CTAs share an SM (one mixes while the other multiplies)
+    if (bn == 64 && pl.mt == 1 && smem_need(nh, nkv, d, tq, 32, talk) <= TWO_CTAS) {
+      pl.bn = 32;
+      pl.smem = smem_need(nh, nkv, d, tq, 32, talk);
+    }
     return true;
   }
   return false;
@@ -507,6 +521,7 @@ KVF_API int kvf_talking_attention_mma_bf16(
                   (bf16*)out, qsl, ctx_lens, nh, dv, out_stride, split_size, max_splits);
   }
   dim3 grid((max_q_len + pl.tq - 1) / pl.tq, B);
+  if (d == 64 && pl.bn == 32) return launch_mma<64, 32, 1, false>(p, grid, pl.smem, st);
   if (d == 64)
     return pl.mt == 1 ? launch_mma<64, 64, 1, false>(p, grid, pl.smem, st) : launch_mma<64, 64, 2, false>(p, grid, pl.smem, st);
   return launch_mma<128, 32, 1, false>(p, grid, pl.smem, st);

@@ -277,7 +277,7 @@ def mixer_weights(g, width, m, dtype):
     "nh,nkv,d,dv,rot,t,bs",
     [(6, 3, 24, 24, 8, 45, 4), (4, 4, 64, 64, 64, 200, 16), (8, 2, 128, 128, 32, 150, 8), (1, 1, 16, 8, 0, 70, 4), (20, 4, 8, 8, 8, 90, 32), (3, 1, 96, 96, 24, 300, 64),
      (32, 8, 64, 64, 32, 330, 16), (24, 8, 128, 128, 64, 210, 16), (12, 4, 64, 64, 16, 140, 8), (16, 1, 64, 64, 0, 97, 4), (64, 8, 64, 64, 64, 80, 32),
-     (1, 1, 128, 128, 128, 170, 16), (40, 8, 64, 64, 32, 75, 16), (2, 2, 64, 32, 32, 60, 8)],
+     (1, 1, 128, 128, 128, 170, 16), (40, 8, 64, 64, 32, 75, 16), (2, 2, 64, 32, 32, 60, 8), (16, 16, 64, 64, 32, 100, 16)],
 )  # fmt: skip
 def test_attention_whose_heads_talk(dtype, nh, nkv, d, dv, rot, t, bs):
     """The whole sequence in one step, then portions and single tokens on top of the cache (the decode form: key
