@@ -106,15 +106,20 @@ class RoutedExperts(FeedForward):
         if resid is not None and resid.shape[0] >= n and resid.shape[1] == self.hidden:
             ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, resid[:n], rt.err, self.activation)
             return self.shared.forward(ctx, x) if self.shared is not None else ops.ADDED
+        if self.shared is not None:
+            # the shared expert first: when its result comes as the float slices of a split product, the routed sum is
+            # added into the first slice and the slices are handed on as they are (whoever reads them adds them in order)
+            y = self.shared.forward(ctx, x)
+            if isinstance(y, ops.Partials) and y.t.dtype == torch.float32 and y.t.shape[1] >= n and y.t.shape[2] == self.hidden:
+                ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, y.t[0, :n], rt.err, self.activation)
+                return y
+            out = rt.buf("experts.out", n, self.hidden, torch.float32)
+            out.zero_()
+            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out, rt.err, self.activation)
+            if y is not None and y is not ops.ADDED:
+                ops.add_residual(out, y[:n])
+            return ops.Partials(out.view(1, n, self.hidden))
         out = rt.buf("experts.out", n, self.hidden, torch.float32)
         out.zero_()
         ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out, rt.err, self.activation)
-        if self.shared is not None:
-            # the shared expert's result joins the routed sum in 32-bit
-            y = self.shared.forward(ctx, x)
-            if isinstance(y, ops.Partials):
-                for s in range(y.nsplit):
-                    ops.add_residual(out, y.t[s, :n])
-            elif y is not None and y is not ops.ADDED:
-                ops.add_residual(out, y[:n])
         return ops.Partials(out.view(1, n, self.hidden))
