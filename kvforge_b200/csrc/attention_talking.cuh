@@ -1,5 +1,5 @@
 // Paged grouped-query attention whose heads talk to one another before the softmax, with an optional
-// sink in the softmax, on the FP32 pipes: any head size (a multiple of 8 up to 256), up to 64 heads, any
+// sink in the softmax, on the FP32 pipes: any head size up to 256, up to 64 heads, any
 // grouping, any mix of query lengths in one flat batch.
 //
 // What it computes, for query i of sequence b at position p = ctx_b - q_b + i and key j <= p
@@ -72,11 +72,25 @@ template <> __device__ __forceinline__ void load_vec<bf16>(const bf16* src, floa
 }
 
 // `count` tiles of TK keys from position t0 on, of kv heads c0 .. c0 + count - 1, `width` numbers a key, as
-// float rows of `ld`; keys at or beyond ctx and pages that were given back are zeros.
+// float rows of `ld`; keys at or beyond ctx and pages that were given back are zeros.  A width that is no multiple
+// of a 16-byte load goes number by number, and the row is filled with zeros up to the next multiple of four.
 template <typename T>
 __device__ __forceinline__ void stage_tiles(const T* cache, const int* bt, int t0, int ctx, int c0, int count, int width,
                                             int ld, int nkv, int block_size, float* dst) {
   constexpr int VN = Vec<T>::N;
+  if (width % VN != 0) {
+    const int wpad = (width + 3) & ~3;
+    for (int idx = threadIdx.x; idx < count * TK * wpad; idx += blockDim.x) {
+      const int cc = idx / (TK * wpad), rem = idx - cc * TK * wpad;
+      const int key = rem / wpad, col = rem - key * wpad;
+      const int kp = t0 + key;
+      const int blk = (kp < ctx && col < width) ? bt[kp / block_size] : -1;
+      float f = 0.f;
+      if (blk >= 0) f = to_float<T>(cache[(((size_t)blk * nkv + (c0 + cc)) * block_size + (kp % block_size)) * width + col]);
+      dst[((size_t)cc * TK + key) * ld + col] = f;
+    }
+    return;
+  }
   const int per = width / VN;
   for (int idx = threadIdx.x; idx < count * TK * per; idx += blockDim.x) {
     const int cc = idx / (TK * per), rem = idx - cc * TK * per;
@@ -105,9 +119,10 @@ __global__ void __launch_bounds__(NW * 32) talking_attention_kernel(const TalkPa
   const int d = p.d, dv = p.dv, nh = p.nh, tq = p.tq;
   const int R = nh * tq;
   const int nhp = (nh + 3) & ~3;
-  const int ld = (d > dv ? d : dv) + 4;
-  float* Qs = smem;                                  // [R][d]
-  float* Ss = Qs + (size_t)R * d;                    // [R][TK]
+  const int dp = (d + 3) & ~3;  // a query row and a key row are walked four numbers at a time: zeros fill them up
+  const int ld = (((d > dv ? d : dv) + 3) & ~3) + 4;
+  float* Qs = smem;                                  // [R][dp]
+  float* Ss = Qs + (size_t)R * dp;                   // [R][TK]
   float* Ps = p.talk ? Ss + (size_t)R * TK : Ss;     // [R][TK]
   float* Tt = Ps + (size_t)R * TK;                   // [nh][nhp]: Tt[g][h] = talk[h][g]
   float* KVs = p.talk ? Tt + (size_t)nh * nhp : Tt;  // [gc][TK][ld]
@@ -136,10 +151,10 @@ __global__ void __launch_bounds__(NW * 32) talking_attention_kernel(const TalkPa
 
   // ---- stage the queries as float, and the mixing matrix turned (source head first)
   const T* qg = (const T*)p.q;
-  for (int idx = threadIdx.x; idx < R * d; idx += blockDim.x) {
-    const int r = idx / d, j = idx - r * d;
+  for (int idx = threadIdx.x; idx < R * dp; idx += blockDim.x) {
+    const int r = idx / dp, j = idx - r * dp;
     const int h = r / tq, i = r - h * tq;
-    Qs[idx] = i < n_tok ? to_float<T>(qg[(size_t)(q_begin + q0 + i) * p.q_stride + (size_t)h * d + j]) : 0.f;
+    Qs[idx] = (i < n_tok && j < d) ? to_float<T>(qg[(size_t)(q_begin + q0 + i) * p.q_stride + (size_t)h * d + j]) : 0.f;
   }
   if (p.talk)
     for (int idx = threadIdx.x; idx < nh * nhp; idx += blockDim.x) {
@@ -191,9 +206,9 @@ __global__ void __launch_bounds__(NW * 32) talking_attention_kernel(const TalkPa
         const int c = h / gs;
         if (r >= R || r - h * tq >= n_tok || c < c0 || c >= c0 + cn) continue;  // warp-uniform
         const float* krow = KVs + ((size_t)(c - c0) * TK + lane) * ld;
-        const float* qrow = Qs + (size_t)r * d;
+        const float* qrow = Qs + (size_t)r * dp;
         float s = 0.f;
-        for (int c = 0; c < d; c += 4) {
+        for (int c = 0; c < dp; c += 4) {
           const float4 k4 = *reinterpret_cast<const float4*>(krow + c);
           const float4 q4 = *reinterpret_cast<const float4*>(qrow + c);
           s = fmaf(q4.x, k4.x, s);
@@ -395,7 +410,7 @@ int talking_attention(const void* q, void* out, const void* kcache, const void* 
                       float scale, int window, int split_size, int max_splits, int grid_splits, float* part_acc,
                       float* part_ml, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
-  if (d <= 0 || d > 256 || (d % 8) != 0 || dv <= 0 || dv > 256 || (dv % 8) != 0 || nkv <= 0 || nh % nkv != 0 ||
+  if (d <= 0 || d > 256 || dv <= 0 || dv > 256 || nkv <= 0 || nh % nkv != 0 ||
       nh > NW * MAXR || block_size <= 0 || (unsigned)B > 65535u)
     return (int)cudaErrorInvalidValue;
   TalkParams p;
@@ -407,7 +422,8 @@ int talking_attention(const void* q, void* out, const void* kcache, const void* 
   p.window = window; p.scale = scale; p.split_size = split_size; p.max_splits = max_splits;
   const bool split = split_size > 0;
   if (split && (split_size % TK != 0 || max_splits <= 0 || !part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
-  const int ld = (d > dv ? d : dv) + 4;
+  const int dp = (d + 3) & ~3;
+  const int ld = (((d > dv ? d : dv) + 3) & ~3) + 4;
   const int nhp = (nh + 3) & ~3;
   const size_t tile = (size_t)TK * ld * sizeof(float);
   int tq = split ? 1 : (NW * MAXR) / nh;
@@ -416,7 +432,7 @@ int talking_attention(const void* q, void* out, const void* kcache, const void* 
   size_t fixed = 0;
   for (;; --tq) {  // fewer queries per CTA until the rows and one tile fit
     const size_t R = (size_t)nh * tq;
-    fixed = (R * d + (talk ? 2 : 1) * R * TK + (talk ? (size_t)nh * nhp : 0)) * sizeof(float);
+    fixed = (R * dp + (talk ? 2 : 1) * R * TK + (talk ? (size_t)nh * nhp : 0)) * sizeof(float);
     if (fixed + tile <= SMEM_HARD || tq == 1) break;
   }
   if (fixed + tile > SMEM_HARD) return (int)cudaErrorInvalidValue;

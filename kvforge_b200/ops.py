@@ -1765,6 +1765,7 @@ def scale_softcap(logits: torch.Tensor, scale: float, cap: float) -> None:
 
 
 TALKING_MAX_HEADS = 64  # what the kernel's CTA of eight warps holds: a row per (head, query), eight rows a warp
+TALKING_MAX_HEAD_DIM = 256  # any size up to here: sizes that are no multiple of a 16-byte load go number by number
 TALKING_MMA_RANGE_STEP = 32  # keys per tile of the tensor-core form's key ranges
 
 _talking_mma_known: dict[tuple, bool] = {}

@@ -46,8 +46,8 @@ class TalkingAttention(Mixer):
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if self.nh > ops.TALKING_MAX_HEADS:
             raise ValueError(f"attention whose heads talk takes at most {ops.TALKING_MAX_HEADS} heads")
-        ops.check_head_dim(self.d)
-        ops.check_head_dim(self.dv)
+        if not 0 < self.dv <= ops.TALKING_MAX_HEAD_DIM or not 0 < self.d <= ops.TALKING_MAX_HEAD_DIM:
+            raise ValueError(f"attention whose heads talk takes heads of 1 to {ops.TALKING_MAX_HEAD_DIM} numbers")
         self.values = params.get("values", "projection")
         if self.values not in ("keys", "projection"):
             raise ValueError("values must be 'keys' or 'projection'")

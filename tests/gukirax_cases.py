@@ -2,7 +2,7 @@
 package's random-weights mode), and the plain implementation's logits for them.
 
 The configurations differ from one another in every size and option: heads and key heads (equal, several
-heads a key head, a single key head), head sizes (8 to 128), value sizes (equal to the key's and smaller), how
+heads a key head, a single key head), head sizes (8 to 128, and sizes that are no multiple of 8), value sizes (equal to the key's and smaller), how
 many dims turn (none, some, all), layers with a dense feed-forward, with experts (one a token, several; with
 and without a shared expert) and without any, a loop from the first layer, in the middle, to the last layer,
 over a single layer, and none, logits scaled and capped or neither.
@@ -91,6 +91,19 @@ CASES: dict[str, dict] = {
         },
         "block_size": 32,
     },
+    # heads whose sizes are no multiple of 8 (12, 20 and 36 numbers), of which 6, 10 and all turn; a width that is one neither
+    "e": {
+        "config": {
+            "architecture": "Gukirax", "vocab": 77, "width": 52, "norm": {"eps": 1e-5}, "logit_scale": 0.7, "logit_softcap": 15.0,
+            "loop": {"start": 0, "stop": 2, "times": 2},
+            "layers": [
+                layer(attention(3, 3, 12, 6), moe(5, 2, 20, 12)),
+                layer(attention(4, 2, 20, 10, base=1000.0), dense(44)),
+                layer(attention(2, 1, 36, 36), None),
+            ],
+        },
+        "block_size": 8,
+    },
 }  # fmt: skip
 
 
@@ -162,7 +175,7 @@ def plain_logits(config: dict, tensors: dict[str, torch.Tensor], tokens: list[in
 
 def random_config(seed: int) -> dict:
     """A configuration drawn at random: widths that are and are not multiples of 16, one to twenty heads in any
-    grouping, head sizes from 8 to 128, values as wide as keys or narrower, any even number of turning dims, dense
+    grouping, head sizes from 8 to 128 (multiples of 8 and not), values as wide as keys or narrower, any even number of turning dims, dense
     layers, experts with and without a shared one, layers without a feed-forward, a loop over any stretch (or none)
     with one to three passes."""
     rng = random.Random(seed)
@@ -174,7 +187,7 @@ def random_config(seed: int) -> dict:
     for _ in range(n_layers):
         kv = rng.choice([1, 2, 3, 4])
         heads = kv * rng.choice([1, 2, 3, 5])
-        dim = rng.choice([8, 16, 24, 40, 64, 96, 128])
+        dim = rng.choice([8, 12, 16, 20, 24, 40, 64, 96, 128])
         vdim = dim if rng.random() < 0.6 else 8 * rng.randint(1, dim // 8)
         rot = 2 * rng.randint(0, dim // 2)
         mixer = attention(heads, kv, dim, rot, vdim, base=rng.choice([100.0, 10000.0, 1e6]), scale=rng.uniform(0.05, 0.4))

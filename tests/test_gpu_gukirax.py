@@ -25,7 +25,7 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 TOL = {"float32": 1e-4, "bfloat16": 0.25}
 SHARP_TOL = 1e-3
-LENGTHS = {"a": [70, 3, 41, 1, 26, 97], "b": [9, 120, 33, 2, 64, 50], "c": [45, 17, 5, 80, 30], "d": [130, 20, 75, 49, 9]}
+LENGTHS = {"a": [70, 3, 41, 1, 26, 97], "b": [9, 120, 33, 2, 64, 50], "c": [45, 17, 5, 80, 30], "d": [130, 20, 75, 49, 9], "e": [66, 2, 31, 90]}
 # the router's logits are spread wide where activations are rounded to bfloat16: a token's last chosen expert then
 # carries little weight, and a choice that rounding turns moves the logits by little
 SPREAD = {"float32": 1.5, "bfloat16": 5.0}
@@ -277,7 +277,8 @@ def mixer_weights(g, width, m, dtype):
     "nh,nkv,d,dv,rot,t,bs",
     [(6, 3, 24, 24, 8, 45, 4), (4, 4, 64, 64, 64, 200, 16), (8, 2, 128, 128, 32, 150, 8), (1, 1, 16, 8, 0, 70, 4), (20, 4, 8, 8, 8, 90, 32), (3, 1, 96, 96, 24, 300, 64),
      (32, 8, 64, 64, 32, 330, 16), (24, 8, 128, 128, 64, 210, 16), (12, 4, 64, 64, 16, 140, 8), (16, 1, 64, 64, 0, 97, 4), (64, 8, 64, 64, 64, 80, 32),
-     (1, 1, 128, 128, 128, 170, 16), (40, 8, 64, 64, 32, 75, 16), (2, 2, 64, 32, 32, 60, 8), (16, 16, 64, 64, 32, 100, 16)],
+     (1, 1, 128, 128, 128, 170, 16), (40, 8, 64, 64, 32, 75, 16), (2, 2, 64, 32, 32, 60, 8), (16, 16, 64, 64, 32, 100, 16),
+     (5, 5, 12, 12, 6, 60, 4), (3, 1, 20, 20, 10, 90, 8), (2, 2, 36, 36, 36, 70, 16), (4, 2, 100, 100, 50, 50, 4), (2, 1, 6, 6, 2, 40, 4)],
 )  # fmt: skip
 def test_attention_whose_heads_talk(dtype, nh, nkv, d, dv, rot, t, bs):
     """The whole sequence in one step, then portions and single tokens on top of the cache (the decode form: key
