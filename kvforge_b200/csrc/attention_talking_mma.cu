@@ -9,8 +9,8 @@
 //   1. the key tiles of every kv head are in shared memory (cp.async, issued one tile ahead); every warp
 //      computes its rows' scores and writes them, scaled, as floats S[head][query][key];
 //   2. the value tiles are on their way; the heads are mixed, S'[h] = sum_g talk[h][g] S[g], source heads in
-//      order: a warp owns eight target heads of 32 or 128 (query, key) columns and keeps the matrix's row in
-//      registers while it walks its columns;
+//      order: a warp owns eight target heads of 32, 64 or 128 (query, key) columns (as many as still leave every
+//      warp its share) and keeps the matrix's row in registers while it walks its columns;
 //   3. every warp reads its rows of S' back in the accumulator layout, masks, moves the running maximum and
 //      sum on (the sink is where they start) and adds weights x values; the weights enter that product as two
 //      bfloat16 terms (the rounded weight and the rounded rest), so 16 bits of them count.
@@ -311,9 +311,12 @@ __global__ void __launch_bounds__(NW * 32, (D == 64 && BN == 32 && MT == 1) ? 2 
       cp_async_commit();
     }
     // ---- 2. the heads talk
-    if (p.talk) {
-      if ((tq * BN) % 128 == 0)
+    if (p.talk) {  // as many columns a lane as still leave every warp an item
+      const int cols32 = tq * BN / 32, chunks = nhp / HC;
+      if (cols32 % 4 == 0 && chunks * (cols32 / 4) >= NW)
         mix_heads<BN, BNP, 4>(Ss, Ps, Tt, nh, nhp, tq, warp, lane);
+      else if (cols32 % 2 == 0 && chunks * (cols32 / 2) >= NW)
+        mix_heads<BN, BNP, 2>(Ss, Ps, Tt, nh, nhp, tq, warp, lane);
       else
         mix_heads<BN, BNP, 1>(Ss, Ps, Tt, nh, nhp, tq, warp, lane);
     }
