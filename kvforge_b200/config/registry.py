@@ -78,6 +78,11 @@ def _ensure_builtin() -> None:
 
     if GUKIRAX not in ARCHITECTURES:
         register_architecture(GUKIRAX, GukiraxConfig.from_dict, gukirax_spec)
+    from ..models.sonalix import sonalix_spec
+    from .sonalix_config import ARCHITECTURE as SONALIX, SonalixConfig
+
+    if SONALIX not in ARCHITECTURES:
+        register_architecture(SONALIX, SonalixConfig.from_dict, sonalix_spec)
 
 
 _LLAMA3_32 = RopeScaling(factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)
@@ -126,3 +131,7 @@ PRESETS.update(SETENEX_PRESETS)
 from .gukirax_config import GUKIRAX_PRESETS  # noqa: E402
 
 PRESETS.update(GUKIRAX_PRESETS)
+
+from .sonalix_config import SONALIX_PRESETS  # noqa: E402
+
+PRESETS.update(SONALIX_PRESETS)

@@ -10,6 +10,9 @@
 // visible at any distance).  S = scale * (q . k) in float, plus, when a table is given, a learned
 // bias by distance: bias[head][min(p - j, far)], `bias` float [nh][far + 1] (a head's values for
 // neighbouring keys lie side by side); softmax in float, O = P V in float, one rounding to T.
+// With softcap c > 0 the scaled score becomes c * tanh(S / c) (before any bias).  With `sinks` (float [nh])
+// the softmax's denominator also holds exp(sinks[head]): a learned number a head that has no key and no
+// value, is neither scaled nor capped, and counts once however the keys are cut into ranges.
 //
 // Exactness: keys are walked in tiles of 32 that start at absolute positions (multiples
 // of 32), each score is one thread's sequential dot product, and a fully masked tile
@@ -50,6 +53,8 @@ struct AttnParams {
   int bias_far;
   int split_size, max_splits;
   float scale;
+  float softcap;          // 0: scores are left as they are
+  const float* sinks;     // [nh] or null
 };
 
 template <typename T> struct Vec;
@@ -209,6 +214,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
       float sc = -INFINITY;
       if (vis) {
         sc = s[i] * p.scale;
+        if (p.softcap > 0.f) sc = p.softcap * tanhf(sc / p.softcap);
         if (p.bias) sc += __ldg(p.bias + (size_t)hd[i] * (p.bias_far + 1) + min(pos[i] - kp, p.bias_far));
       }
       const float tmax = warp_max(sc);
@@ -265,7 +271,13 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_generic_kernel(const At
         if (dim < dv) p.part_acc[slot * dv + dim] = acc[i][e];
       }
     } else {
-      const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+      float lsum = l[i], corr = 1.f;
+      if (p.sinks) {  // the sink joins the denominator once, after every key
+        const float sk = p.sinks[head], mm = fmaxf(m[i], sk);
+        corr = m[i] == -INFINITY ? 0.f : expf(m[i] - mm);
+        lsum = l[i] * corr + expf(sk - mm);
+      }
+      const float inv = lsum > 0.f ? corr / lsum : 0.f;
       T* o = (T*)p.out + (size_t)(q_begin + q0 + tok) * p.out_stride + (size_t)head * dv;
 #pragma unroll
       for (int e = 0; e < DPL; ++e) {
@@ -281,7 +293,7 @@ template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                     T* __restrict__ out, const int* __restrict__ qsl,
                                     const int* __restrict__ ctx_lens, int nh, int d, int out_stride,
-                                    int split_size, int max_splits) {
+                                    int split_size, int max_splits, const float* __restrict__ sinks) {
   const int b = blockIdx.y, head = blockIdx.x;
   const int q_begin = qsl[b], q_len = qsl[b + 1] - q_begin;
   const int ctx = ctx_lens[b];
@@ -290,7 +302,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_acc, const fl
   const size_t base = ((size_t)b * nh + head) * max_splits;
   float M = -INFINITY;
   for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  float L = 0.f;
+  if (sinks) M = fmaxf(M, sinks[head]);
+  float L = sinks ? expf(sinks[head] - M) : 0.f;
   for (int s = 0; s < ns; ++s) {
     const float ms = part_ml[(base + s) * 2];
     if (ms != -INFINITY) L += expf(ms - M) * part_ml[(base + s) * 2 + 1];
@@ -334,8 +347,9 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
                             int max_q_len, int q_stride, int out_stride, int bt_stride, int nh, int nkv,
                             int d, int dv, int block_size, float scale, int window, int split_size, int max_splits,
                             int grid_splits, float* part_acc, float* part_ml, int keep_first, int v_stride,
-                            const float* bias, int bias_far, cudaStream_t st) {
+                            const float* bias, int bias_far, float softcap, const float* sinks, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
+  if (softcap < 0.f) return (int)cudaErrorInvalidValue;
   if (dv <= 0) dv = d;
   if (v_stride <= 0) v_stride = dv;
   if (d <= 0 || d > 1024 || (d % 8) != 0 || dv > 512 || (dv % 8) != 0 || nkv <= 0 || nh % nkv != 0 || block_size <= 0)
@@ -356,6 +370,7 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
   p.window = window; p.scale = scale;
   p.keep_first = window > 0 ? keep_first : 0; p.v_stride = v_stride;
   p.bias = bias; p.bias_far = bias_far;
+  p.softcap = softcap; p.sinks = sinks;
   p.split_size = split_size; p.max_splits = max_splits;
   if ((unsigned)B > 65535u || (unsigned)(nkv * p.chunks) > 65535u) return (int)cudaErrorInvalidValue;
   if (split_size > 0) {
@@ -367,7 +382,7 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
     int rc = dispatch_dpl<T, true>(p, grid, st);
     if (rc) return rc;
     attn_combine_kernel<T><<<dim3(nh, B), 64, 0, st>>>(part_acc, part_ml, (T*)out, qsl, ctx_lens, nh, dv,
-                                                       out_stride, split_size, max_splits);
+                                                       out_stride, split_size, max_splits, sinks);
     return KVF_LAUNCH_STATUS();
   }
   dim3 grid((max_q_len + p.tq - 1) / p.tq, B, nkv * p.chunks);
@@ -382,11 +397,11 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
       const int* qsl, const int* ctx_lens, int B, int max_q_len, int q_stride, int out_stride,            \
       int bt_stride, int nh, int nkv, int d, int dv, int block_size, float scale, int window,             \
       int split_size, int max_splits, int grid_splits, float* part_acc, float* part_ml, int keep_first,   \
-      int v_stride, const float* bias, int bias_far, cudaStream_t st) {                                   \
+      int v_stride, const float* bias, int bias_far, float softcap, const float* sinks, cudaStream_t st) { \
     return paged_attention_generic<T>(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len,  \
                                       q_stride, out_stride, bt_stride, nh, nkv, d, dv, block_size, scale, \
                                       window, split_size, max_splits, grid_splits, part_acc, part_ml,     \
-                                      keep_first, v_stride, bias, bias_far, st);                          \
+                                      keep_first, v_stride, bias, bias_far, softcap, sinks, st);          \
   }
 
 KVF_ATTN_API(f32, float)

@@ -1,9 +1,13 @@
 // A feed-forward made of many small experts of which every token uses a few.
 //
-//   route   : per token the router's logits (float), scores s = 1 / (1 + exp(-z)), the choice among
-//             the best groups of neighbouring experts, the chosen experts and their weights
+//   route   : per token the router's logits (float, plus a bias per expert where the router has one), scores
+//             s = 1 / (1 + exp(-z)) (or a softmax over all experts, or the logits themselves with a softmax
+//             over the chosen ones alone), the choice among the best groups of neighbouring experts, the
+//             chosen experts and their weights
 //   sort    : the (token, choice) pairs ordered by expert, and the list of row tiles per expert
-//   product : for every tile of one expert's rows a tile of  act(x W_up^T)  or of  h W_down^T
+//   product : for every tile of one expert's rows a tile of  act(x W_up^T)  or of  h W_down^T; a gated expert's
+//             first matrix holds gate and up rows in alternating blocks of 8 and its activation joins the two:
+//             g' = min(g, limit), u' = clamp(u, -limit, limit), g' / (1 + exp(-alpha g')) * (u' + shift)
 //   combine : resid[token] += sum_k weight_k * y[token, k]   (float, k in order)
 //
 // A pair's row of a product depends on that row and on its expert's weights alone (its products are
@@ -50,7 +54,8 @@ template <typename T, int RT>
 __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x, long long x_stride,
                                                          const float* __restrict__ router, const float* __restrict__ correction,
                                                          int n_tokens, int W, int E, int top, int groups, int keep,
-                                                         float norm_eps, int vec, int flags, int* __restrict__ ids, float* __restrict__ wts) {
+                                                         float norm_eps, int vec, int flags, int* __restrict__ ids, float* __restrict__ wts,
+                                                         const float* __restrict__ logit_bias) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float sm[];
@@ -85,10 +90,11 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
     }
 #pragma unroll
     for (int t = 0; t < RT; ++t) {
-      const float zt = warp_sum(z[t]);
+      const float zt = warp_sum(z[t]) + (logit_bias ? logit_bias[e] : 0.f);
       if (lane == 0) {
-        // flags bit 0: the scores are a softmax over all experts, made below from the logits kept here
-        const float s = (flags & 1) ? zt : 1.f / (1.f + expf(-zt));
+        // flags bit 0: the scores are a softmax over all experts, made below from the logits kept here;
+        // bit 2: the logits themselves rank the experts, and the weights are a softmax over the chosen logits
+        const float s = (flags & 5) ? zt : 1.f / (1.f + expf(-zt));
         sm[t * per_token + e] = s;
         sm[t * per_token + E + e] = s + (correction ? correction[e] : 0.f);
       }
@@ -176,6 +182,15 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ x,
     }
     __syncwarp();
   }
+  if (flags & 4) {
+    // softmax over the chosen logits alone: the first chosen is the largest; every lane adds in the order of k
+    const float mx = my_w[0];
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) sum += expf(my_w[k] - mx);
+    __syncwarp();
+    for (int k = lane; k < top; k += 32) my_w[k] = expf(my_w[k] - mx) / sum;
+    return;
+  }
   if (flags & 2) return;  // the weights are the chosen scores as they are
   const float inv = 1.f / (total + norm_eps);
   for (int k = lane; k < top; k += 32) my_w[k] *= inv;
@@ -224,7 +239,18 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
 }
 
 __device__ __forceinline__ float gelu_erf(float z) { return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f)); }
-// an expert's activation: 0 the exact GELU, 1 the square of relu
+// What an expert applies between its two products.  kind 0: the exact GELU, 1: the square of relu, 2: gated (the
+// first matrix holds gate and up rows in alternating blocks of 8; see `gated_act`).
+struct ExpertAct {
+  int kind;
+  float limit, alpha, shift;
+};
+constexpr int ACT_GATED = 2;
+__device__ __forceinline__ float gated_act(float g, float u, const ExpertAct& a) {
+  g = fminf(g, a.limit);
+  u = fminf(fmaxf(u, -a.limit), a.limit);
+  return g / (1.f + expf(-a.alpha * g)) * (u + a.shift);
+}
 __device__ __forceinline__ float expert_act(float z, int kind) {
   if (kind == 1) {
     const float r = fmaxf(z, 0.f);
@@ -240,7 +266,7 @@ template <typename T, bool UP>
 __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ a, long long a_stride, const T* __restrict__ w,
                                                            const int* __restrict__ order, const int* __restrict__ tiles,
                                                            const int* __restrict__ meta, int top, int K, int n_out,
-                                                           T* __restrict__ act, float* __restrict__ y, int act_kind) {
+                                                           T* __restrict__ act, float* __restrict__ y, ExpertAct ea, int act_ld) {
   pdl_launch();
   pdl_wait();
   constexpr int BN = 64, BK = 16;
@@ -258,7 +284,10 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
   }
   __syncthreads();
   const T* wb = w + (size_t)e * n_out * K;
-  const int ty = tid >> 4, tx = tid & 15;  // rows ty*2 .. +1, columns tx*4 .. +3
+  // rows ty*2 .. +1; columns cb, cb+1 and cb+8, cb+9 of the tile: with gate and up rows in blocks of 8 a thread
+  // holds two gates and their ups
+  const int ty = tid >> 4, tx = tid & 15;
+  const int cb = (tx >> 2) * 16 + (tx & 3) * 2;
   float acc[2][4] = {};
   for (int k0 = 0; k0 < K; k0 += BK) {
     for (int idx = tid; idx < TM * BK; idx += 256) {
@@ -279,7 +308,7 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
       const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float b = Bs[kk][tx * 4 + j];
+        const float b = Bs[kk][cb + (j & 1) + 8 * (j >> 1)];
         acc[0][j] = fmaf(a0, b, acc[0][j]);
         acc[1][j] = fmaf(a1, b, acc[1][j]);
       }
@@ -290,12 +319,21 @@ __global__ void __launch_bounds__(256) moe_product_kernel(const T* __restrict__ 
   for (int i = 0; i < 2; ++i) {
     const int r = ty * 2 + i;
     if (r >= rows) continue;
+    if (UP && ea.kind == ACT_GATED) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int c = col0 + cb + j;  // a gate row of the stacked matrix; its up row is 8 further
+        if (c + 8 >= n_out) continue;
+        act[(size_t)(row0 + r) * act_ld + (c >> 4) * 8 + (c & 7)] = from_float<T>(gated_act(acc[i][j], acc[i][j + 2], ea));
+      }
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int c = col0 + tx * 4 + j;
+      const int c = col0 + cb + (j & 1) + 8 * (j >> 1);
       if (c >= n_out) continue;
       if (UP)
-        act[(size_t)(row0 + r) * n_out + c] = from_float<T>(expert_act(acc[i][j], act_kind));
+        act[(size_t)(row0 + r) * act_ld + c] = from_float<T>(expert_act(acc[i][j], ea.kind));
       else
         y[(size_t)order[row0 + r] * n_out + c] = acc[i][j];
     }
@@ -331,7 +369,7 @@ template <int NT, int STAGES, bool UP>
 __global__ void __launch_bounds__(128) moe_product_mma_kernel(const bf16* __restrict__ a, long long a_stride, const bf16* __restrict__ w,
                                                                const int* __restrict__ order, const int* __restrict__ tiles,
                                                                const int* __restrict__ meta, int top, int K, int n_out,
-                                                               bf16* __restrict__ act, float* __restrict__ y, int act_kind) {
+                                                               bf16* __restrict__ act, float* __restrict__ y, ExpertAct ea, int act_ld) {
   constexpr int BN = 64, BK = 64, THREADS = 128;
   constexpr int W_BYTES = BN * 128, X_ROWS = NT * 8, X_BYTES = X_ROWS * 128, STAGE_BYTES = W_BYTES + X_BYTES;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -411,13 +449,18 @@ __global__ void __launch_bounds__(128) moe_product_mma_kernel(const bf16* __rest
     for (int r = 0; r < 2; ++r) {
       const int t = j * 8 + ((lane & 3) << 1) + r;
       if (t >= rows) continue;
+      if (UP && ea.kind == ACT_GATED) {
+        // stacked rows f0 (a gate) and f0 + 8 (its up): one output column
+        if (f0 + 8 < n_out) act[(size_t)dst[t] * act_ld + (f0 >> 4) * 8 + (f0 & 7)] = __float2bfloat16_rn(gated_act(acc[j][r], acc[j][2 + r], ea));
+        continue;
+      }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int f = f0 + 8 * h;
         if (f >= n_out) continue;
         const float v = acc[j][2 * h + r];
         if (UP)
-          act[(size_t)dst[t] * n_out + f] = __float2bfloat16_rn(expert_act(v, act_kind));
+          act[(size_t)dst[t] * act_ld + f] = __float2bfloat16_rn(expert_act(v, ea.kind));
         else
           y[(size_t)dst[t] * n_out + f] = v;
       }
@@ -427,23 +470,23 @@ __global__ void __launch_bounds__(128) moe_product_mma_kernel(const bf16* __rest
 
 template <int NT, int STAGES, bool UP>
 int launch_mma(const bf16* a, long long a_stride, const bf16* w, const int* order, const int* tiles, const int* meta, int top, int K,
-               int n_out, int max_tiles, bf16* act, float* y, int act_kind, cudaStream_t st) {
+               int n_out, int max_tiles, bf16* act, float* y, ExpertAct ea, int act_ld, cudaStream_t st) {
   const size_t smem = (size_t)STAGES * (64 * 128 + NT * 8 * 128);
   auto kern = moe_product_mma_kernel<NT, STAGES, UP>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch(kern, dim3((n_out + 63) / 64, max_tiles), dim3(128), smem, st, a, a_stride, w, order, tiles, meta, top, K, n_out, act, y, act_kind);
+  return launch(kern, dim3((n_out + 63) / 64, max_tiles), dim3(128), smem, st, a, a_stride, w, order, tiles, meta, top, K, n_out, act, y, ea, act_ld);
 }
 
 template <bool UP>
 int product_mma(int tm, const bf16* a, long long a_stride, const bf16* w, const int* order, const int* tiles, const int* meta, int top, int K,
-                int n_out, int max_tiles, bf16* act, float* y, int act_kind, cudaStream_t st) {
-  if (tm <= 8) return launch_mma<1, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, act_kind, st);
-  if (tm <= 16) return launch_mma<2, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, act_kind, st);
-  if (tm <= 32) return launch_mma<4, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, act_kind, st);
-  return launch_mma<8, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, act_kind, st);
+                int n_out, int max_tiles, bf16* act, float* y, ExpertAct ea, int act_ld, cudaStream_t st) {
+  if (tm <= 8) return launch_mma<1, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, ea, act_ld, st);
+  if (tm <= 16) return launch_mma<2, 8, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, ea, act_ld, st);
+  if (tm <= 32) return launch_mma<4, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, ea, act_ld, st);
+  return launch_mma<8, 6, UP>(a, a_stride, w, order, tiles, meta, top, K, n_out, max_tiles, act, y, ea, act_ld, st);
 }
 
 // Rows of a tile for P pairs over E experts on the tensor cores: small tiles while an expert has a few rows (the
@@ -513,45 +556,47 @@ KVF_API int kvf_moe_max_tiles(int n_pairs, int E) { return n_pairs / TM_MIN + E;
 
 template <typename T>
 int run_products(const T* x, long long x_stride, const T* w_up, const T* w_down, const int* ids, int P, int W, int ff, int E, int top,
-                 int* order, int* tiles, int* meta, T* act, float* y, int act_kind, cudaStream_t st);
+                 int* order, int* tiles, int* meta, T* act, float* y, ExpertAct ea, cudaStream_t st);
 
 template <>
 int run_products<float>(const float* x, long long x_stride, const float* w_up, const float* w_down, const int* ids, int P, int W, int ff,
-                        int E, int top, int* order, int* tiles, int* meta, float* act, float* y, int act_kind, cudaStream_t st) {
+                        int E, int top, int* order, int* tiles, int* meta, float* act, float* y, ExpertAct ea, cudaStream_t st) {
   int rc = launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), st, ids, P, E, TM, order, tiles, meta);
   if (rc) return rc;
   const int max_tiles = P / TM + E;
-  rc = launch(moe_product_kernel<float, true>, dim3((ff + 63) / 64, max_tiles), dim3(256), 0, st, x, x_stride, w_up, (const int*)order,
-              (const int*)tiles, (const int*)meta, top, W, ff, act, (float*)nullptr, act_kind);
+  const int n_up = ea.kind == ACT_GATED ? 2 * ff : ff;  // rows of an expert's first matrix
+  rc = launch(moe_product_kernel<float, true>, dim3((n_up + 63) / 64, max_tiles), dim3(256), 0, st, x, x_stride, w_up, (const int*)order,
+              (const int*)tiles, (const int*)meta, top, W, n_up, act, (float*)nullptr, ea, ff);
   if (rc) return rc;
   return launch(moe_product_kernel<float, false>, dim3((W + 63) / 64, max_tiles), dim3(256), 0, st, (const float*)act, (long long)ff,
-                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (float*)nullptr, y, act_kind);
+                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (float*)nullptr, y, ea, ff);
 }
 
 template <>
 int run_products<bf16>(const bf16* x, long long x_stride, const bf16* w_up, const bf16* w_down, const int* ids, int P, int W, int ff, int E,
-                       int top, int* order, int* tiles, int* meta, bf16* act, float* y, int act_kind, cudaStream_t st) {
+                       int top, int* order, int* tiles, int* meta, bf16* act, float* y, ExpertAct ea, cudaStream_t st) {
+  const int n_up = ea.kind == ACT_GATED ? 2 * ff : ff;
   const bool tensor = (W % 8 == 0) && (ff % 8 == 0) && (x_stride % 8 == 0) && ((((uintptr_t)x) & 15) == 0);
   const int tm = tensor ? mma_tile_rows(P, E) : TM;
   int rc = launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), st, ids, P, E, tm, order, tiles, meta);
   if (rc) return rc;
   const int max_tiles = P / tm + E;
   if (tensor) {
-    rc = product_mma<true>(tm, x, x_stride, w_up, order, tiles, meta, top, W, ff, max_tiles, act, nullptr, act_kind, st);
+    rc = product_mma<true>(tm, x, x_stride, w_up, order, tiles, meta, top, W, n_up, max_tiles, act, nullptr, ea, ff, st);
     if (rc) return rc;
-    return product_mma<false>(tm, act, (long long)ff, w_down, order, tiles, meta, top, ff, W, max_tiles, nullptr, y, act_kind, st);
+    return product_mma<false>(tm, act, (long long)ff, w_down, order, tiles, meta, top, ff, W, max_tiles, nullptr, y, ea, ff, st);
   }
-  rc = launch(moe_product_kernel<bf16, true>, dim3((ff + 63) / 64, max_tiles), dim3(256), 0, st, x, x_stride, w_up, (const int*)order,
-              (const int*)tiles, (const int*)meta, top, W, ff, act, (float*)nullptr, act_kind);
+  rc = launch(moe_product_kernel<bf16, true>, dim3((n_up + 63) / 64, max_tiles), dim3(256), 0, st, x, x_stride, w_up, (const int*)order,
+              (const int*)tiles, (const int*)meta, top, W, n_up, act, (float*)nullptr, ea, ff);
   if (rc) return rc;
   return launch(moe_product_kernel<bf16, false>, dim3((W + 63) / 64, max_tiles), dim3(256), 0, st, (const bf16*)act, (long long)ff,
-                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (bf16*)nullptr, y, act_kind);
+                w_down, (const int*)order, (const int*)tiles, (const int*)meta, top, ff, W, (bf16*)nullptr, y, ea, ff);
 }
 
 #define KVF_EXPERTS_API(SUF, T)                                                                                       \
   KVF_API int kvf_moe_route_##SUF(const void* x, long long x_stride, const float* router, const float* correction,    \
                                   int n_tokens, int W, int E, int top, int groups, int keep, float norm_eps,          \
-                                  int flags, int* ids, float* wts, cudaStream_t st) {                                 \
+                                  int flags, int* ids, float* wts, const float* logit_bias, cudaStream_t st) {        \
     if (n_tokens <= 0) return 0;                                                                                      \
     if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||                   \
         top > keep * (E / groups))                                                                                    \
@@ -562,20 +607,23 @@ int run_products<bf16>(const bf16* x, long long x_stride, const bf16* w_up, cons
     const int vec = (W % 8 == 0) && (x_stride % 8 == 0) && ((((uintptr_t)x) | ((uintptr_t)router)) % 16 == 0);        \
     if (rt == 1)                                                                                                      \
       return launch(moe_route_kernel<T, 1>, dim3(n_tokens), dim3(256), smem, st, (const T*)x, x_stride, router,       \
-                    correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, flags, ids, wts);                   \
+                    correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, flags, ids, wts, logit_bias);       \
     return launch(moe_route_kernel<T, 4>, dim3((n_tokens + 3) / 4), dim3(256), smem, st, (const T*)x, x_stride,       \
-                  router, correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, flags, ids, wts);             \
+                  router, correction, n_tokens, W, E, top, groups, keep, norm_eps, vec, flags, ids, wts, logit_bias); \
   }                                                                                                                   \
   KVF_API int kvf_moe_experts_##SUF(const void* x, long long x_stride, const void* w_up, const void* w_down,          \
                                     const int* ids, const float* wts, int n_tokens, int W, int ff, int E, int top,    \
                                     int* order, int* tiles, int* meta, void* act, float* y, float* resid,             \
-                                    int act_kind, cudaStream_t st) {                                                  \
+                                    int act_kind, float act_limit, float act_alpha, float act_shift,                  \
+                                    cudaStream_t st) {                                                                \
     if (n_tokens <= 0) return 0;                                                                                      \
+    if (act_kind == ACT_GATED && (ff & 7)) return (int)cudaErrorInvalidValue; /* gate and up rows in blocks of 8 */   \
+    const ExpertAct ea{act_kind, act_limit, act_alpha, act_shift};                                                    \
     const int P = n_tokens * top;                                                                                     \
     if ((size_t)3 * E * sizeof(int) > 48 * 1024) return (int)cudaErrorInvalidValue;                                   \
     if (kvf_moe_max_tiles(P, E) > 65535) return (int)cudaErrorInvalidValue;                                           \
     int rc = run_products<T>((const T*)x, x_stride, (const T*)w_up, (const T*)w_down, ids, P, W, ff, E, top, order,   \
-                             tiles, meta, (T*)act, y, act_kind, st);                                                  \
+                             tiles, meta, (T*)act, y, ea, st);                                                        \
     if (rc) return rc;                                                                                                \
     const long long total = (long long)n_tokens * W;                                                                  \
     long long g = (total + 255) / 256;                                                                                \

@@ -44,7 +44,10 @@ struct TcParams {
   void* out;
   int M, N, K;
   int ldo;
-  int mode;  // 0: bfloat16 y; 3: bfloat16 silu(g)*u; 4: bfloat16 gelu(y); 5: float y to the rows that `scatter` names; 6: bfloat16 relu(y)^2
+  // 0: bfloat16 y; 3: bfloat16 silu(g)*u; 4: bfloat16 gelu(y); 5: float y to the rows that `scatter` names; 6: bfloat16 relu(y)^2;
+  // 7: as 3 with g' = min(g, limit), u' = clamp(u, -limit, limit) and g' / (1 + exp(-alpha g')) * (u' + shift)
+  int mode;
+  float act_limit, act_alpha, act_shift;
   int* err;
   // grouped form: `tiles` holds (expert, first row, rows) per row tile, meta[0] their number (at most max_row_tiles);
   // N is then the number of output columns of ONE expert
@@ -306,7 +309,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             r[i] = __float_as_uint(z * z);
           }
         }
-        if (p.mode == 3) {
+        if (p.mode == 7) {
+          const float lim = p.act_limit, al = p.act_alpha, sh = p.act_shift;
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float g = fminf(__uint_as_float(r[16 * h + i]), lim);
+              const float u = fminf(fmaxf(__uint_as_float(r[16 * h + 8 + i]), -lim), lim);
+              r[16 * h + i] = __float_as_uint(__fdividef(g, 1.f + __expf(-al * g)) * (u + sh));
+            }
+        }
+        if (p.mode == 3 || p.mode == 7) {
           // columns are weight rows [g0..7, u0..7, g8..15, u8..15]: 16 outputs from 32 columns
           bf16* dst = reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldo + (col >> 1);
           uint32_t o[8];
@@ -316,7 +330,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             for (int i = 0; i < 8; i += 2) {
               const float g0 = __uint_as_float(r[16 * h + i]), g1 = __uint_as_float(r[16 * h + i + 1]);
               const float u0 = __uint_as_float(r[16 * h + 8 + i]), u1 = __uint_as_float(r[16 * h + 8 + i + 1]);
-              o[4 * h + (i >> 1)] = pack2(__fdividef(g0, 1.f + __expf(-g0)) * u0, __fdividef(g1, 1.f + __expf(-g1)) * u1);
+              o[4 * h + (i >> 1)] = p.mode == 7 ? pack2(g0, g1)  // joined above, in the gates' places
+                                                : pack2(__fdividef(g0, 1.f + __expf(-g0)) * u0, __fdividef(g1, 1.f + __expf(-g1)) * u1);
             }
           if (col + 32 <= p.N) {
             *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -420,6 +435,7 @@ KVF_API int kvf_gemm_tcgen05_bf16(const void* x, const void* w, void* out, int M
   if (mode == 3 && (N & 15)) return (int)cudaErrorInvalidValue;
   TcParams p;
   p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.mode = mode; p.err = err;
+  p.act_limit = p.act_alpha = p.act_shift = 0.f;
   p.tiles = nullptr; p.meta = nullptr; p.scatter = nullptr; p.max_row_tiles = 0;
   CUtensorMap mx, mw;
   int rc = make_map(&mx, x, M, K, ldx, BM);
@@ -436,16 +452,21 @@ KVF_API int kvf_gemm_tcgen05_bf16(const void* x, const void* w, void* out, int M
 
 // The grouped form: x [P, K] with its rows ordered by expert, w [E * N, K], `tiles` / `meta` as a sort on the device
 // left them (row tiles of at most 128 rows, at most max_row_tiles of them).  gelu != 0: out bfloat16 [P, N] =
-// act(x w[e]^T) in the order of x (1: the exact GELU, 2: the square of relu); else out float, row i of the product going to row scatter[i] ([*, N]).
+// act(x w[e]^T) in the order of x (1: the exact GELU, 2: the square of relu; 3: out [P, N/2], gate and up rows of w[e] in
+// alternating blocks of 8 joined as g' / (1 + exp(-alpha g')) * (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit),
+// N % 16 == 0); else out float, row i of the product going to row scatter[i] ([*, N]).
 KVF_API int kvf_gemm_grouped_tcgen05_bf16(const void* x, const void* w, void* out, int P, int N, int K, int E, int ldx,
                                           int ldo, int gelu, const int* tiles, const int* meta, const int* scatter,
-                                          int max_row_tiles, int* err, cudaStream_t st) {
+                                          int max_row_tiles, int* err, float act_limit, float act_alpha, float act_shift,
+                                          cudaStream_t st) {
   if (P <= 0 || N <= 0 || E <= 0 || max_row_tiles <= 0) return 0;
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldo & 7) || !tiles || !meta || (!gelu && !scatter)) return (int)cudaErrorInvalidValue;
   if ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) return (int)cudaErrorInvalidValue;
   if ((long long)E * N > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
   TcParams p;
-  p.out = out; p.M = P; p.N = N; p.K = K; p.ldo = ldo; p.mode = gelu == 2 ? 6 : gelu ? 4 : 5; p.err = err;
+  if (gelu == 3 && (N & 15)) return (int)cudaErrorInvalidValue;
+  p.out = out; p.M = P; p.N = N; p.K = K; p.ldo = ldo; p.mode = gelu == 3 ? 7 : gelu == 2 ? 6 : gelu ? 4 : 5; p.err = err;
+  p.act_limit = act_limit; p.act_alpha = act_alpha; p.act_shift = act_shift;
   p.tiles = tiles; p.meta = meta; p.scatter = gelu ? nullptr : scatter; p.max_row_tiles = max_row_tiles;
   CUtensorMap mx, mw;
   int rc = make_map(&mx, x, P, K, ldx, BM);

@@ -11,10 +11,14 @@ namespace {
 // ---------------------------------------------------------------- per-head norm, rotation, cache write
 // Rows of `qkv` hold nh query heads and nkv key heads of dk and nkv value heads of dv.  A warp owns
 // one (token, head).  Query and key heads: x <- x / sqrt(mean(x^2) + eps) * w (w of dk floats shared
-// by all heads; skipped without w), then the first `rot` dims turn in interleaved pairs (2i, 2i+1) by
-// the angle pos * inv_freq[i] (skipped when rot == 0).  Queries are written back in place; keys and
-// values go to their slot of the paged cache ([blocks][nkv][block_size][dk] and [...][dv]); a slot
-// below zero (padding) is skipped, one beyond the pool raises bit 1 of the error flag.
+// by all heads; skipped without w), then the first `rot` dims turn by the angle pos * inv_freq[i], in
+// interleaved pairs (2i, 2i+1) or, with split_pairs, in pairs (i, i + rot/2) (skipped when rot == 0).
+// Queries are written back in place; keys and values go to their slot of the paged cache
+// ([blocks][nkv][block_size][dk] and [...][dv]); a slot below zero (padding) is skipped, one beyond the
+// pool raises bit 1 of the error flag.  Values may be mixed with those that an earlier layer of the same
+// step left for the same token: with v_keep the values as projected are also copied to v_keep[n][nkv*dv];
+// with v_first the value becomes (1 - lambda) v + lambda v_first[n] (lambda = *v_lambda, in float, rounded
+// once) before it is cached.
 template <typename T>
 __global__ void __launch_bounds__(128) head_norm_cache_kernel(T* __restrict__ qkv, long long row_stride,
                                                                const int* __restrict__ positions,
@@ -23,7 +27,9 @@ __global__ void __launch_bounds__(128) head_norm_cache_kernel(T* __restrict__ qk
                                                                const int* __restrict__ slots, T* __restrict__ kcache,
                                                                T* __restrict__ vcache, int n_tokens, int nh, int nkv, int dk,
                                                                int dv, int block_size, long long num_slots,
-                                                               int* __restrict__ err) {
+                                                               int* __restrict__ err, int split_pairs,
+                                                               T* __restrict__ v_keep, const T* __restrict__ v_first,
+                                                               const float* __restrict__ v_lambda) {
   pdl_launch();
   pdl_wait();
   const int heads = nh + 2 * nkv;
@@ -36,6 +42,11 @@ __global__ void __launch_bounds__(128) head_norm_cache_kernel(T* __restrict__ qk
   long long slot = -1;
   if (!is_q) {
     slot = slots ? slots[n] : -1;
+    if (slot < 0 && !is_k && v_keep) {  // a row without a slot still leaves its values for the layers after
+      const int g = h - nh - nkv;
+      const T* src = row + (size_t)(nh + nkv) * dk + (size_t)g * dv;
+      for (int j = lane; j < dv; j += 32) v_keep[(size_t)n * nkv * dv + (size_t)g * dv + j] = src[j];
+    }
     if (slot < 0) return;
     if (slot >= num_slots) {
       if (lane == 0 && err) atomicOr(err, 2);
@@ -46,7 +57,15 @@ __global__ void __launch_bounds__(128) head_norm_cache_kernel(T* __restrict__ qk
     const int g = h - nh - nkv;
     const T* src = row + (size_t)(nh + nkv) * dk + (size_t)g * dv;
     T* dst = vcache + (((size_t)(slot / block_size) * nkv + g) * block_size + (size_t)(slot % block_size)) * dv;
-    for (int j = lane; j < dv; j += 32) dst[j] = src[j];
+    if (v_first) {
+      const float lam = v_lambda[0];
+      const T* first = v_first + (size_t)n * nkv * dv + (size_t)g * dv;
+      for (int j = lane; j < dv; j += 32) dst[j] = from_float<T>(fmaf(lam, to_float<T>(first[j]), (1.f - lam) * to_float<T>(src[j])));
+    } else {
+      for (int j = lane; j < dv; j += 32) dst[j] = src[j];
+    }
+    if (v_keep)
+      for (int j = lane; j < dv; j += 32) v_keep[(size_t)n * nkv * dv + (size_t)g * dv + j] = src[j];
     return;
   }
   T* x = row + (size_t)h * dk;  // key heads follow the query heads with the same size
@@ -68,12 +87,15 @@ __global__ void __launch_bounds__(128) head_norm_cache_kernel(T* __restrict__ qk
     dst = kcache + (((size_t)(slot / block_size) * nkv + g) * block_size + (size_t)(slot % block_size)) * dk;
   }
   for (int i = lane; i < dk / 2; i += 32) {
-    float a = to_float<T>(x[2 * i]), b = to_float<T>(x[2 * i + 1]);
+    // pair i: dims (2i, 2i+1), or (i, i + rot/2) among the dims that turn in split pairs
+    const bool turns = 2 * i < rot;
+    const int ia = (turns && split_pairs) ? i : 2 * i, ib = (turns && split_pairs) ? i + rot / 2 : 2 * i + 1;
+    float a = to_float<T>(x[ia]), b = to_float<T>(x[ib]);
     if (w) {
-      a = a * r * w[2 * i];
-      b = b * r * w[2 * i + 1];
+      a = a * r * w[ia];
+      b = b * r * w[ib];
     }
-    if (2 * i < rot) {
+    if (turns) {
       float sn, cs;
       sincosf(pos * inv_freq[i], &sn, &cs);
       float ya, yb;
@@ -81,9 +103,31 @@ __global__ void __launch_bounds__(128) head_norm_cache_kernel(T* __restrict__ qk
       a = ya;
       b = yb;
     }
-    dst[2 * i] = from_float<T>(a);
-    dst[2 * i + 1] = from_float<T>(b);
+    dst[ia] = from_float<T>(a);
+    dst[ib] = from_float<T>(b);
   }
+}
+
+// ---------------------------------------------------------------- RMS norm of a column range
+// out[n][:] = x[n][0 .. r) / sqrt(mean(x^2) + eps) * w, a warp per row; x rows may be part of wider rows.
+template <typename T>
+__global__ void __launch_bounds__(128) row_rmsnorm_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ w,
+                                                           float eps, long long n_rows, int r, T* __restrict__ out, long long out_stride) {
+  pdl_launch();
+  pdl_wait();
+  const long long n = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (n >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const T* row = x + (size_t)n * x_stride;
+  float ss = 0.f;
+  for (int j = lane; j < r; j += 32) {
+    const float v = to_float<T>(row[j]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)r + eps);
+  T* dst = out + (size_t)n * out_stride;
+  for (int j = lane; j < r; j += 32) dst[j] = from_float<T>(to_float<T>(row[j]) * inv * w[j]);
 }
 
 // ---------------------------------------------------------------- latent keys and values
@@ -94,8 +138,9 @@ __global__ void __launch_bounds__(128) head_norm_cache_kernel(T* __restrict__ qk
 //   the shared key part, turned                     -> cache row [r, r + dr)
 //   every head's turning query part, turned         -> qa[n][h][r .. r + dr)
 // (qa rows hold nh heads of r + dr; their first r numbers are written by whoever folds the key
-// up-projection into the queries).  Pairs are interleaved (2i, 2i+1), i < rot/2, rot <= dr; angles
-// pos * inv_freq[i].  The cache is [blocks][1][block_size][r + dr].
+// up-projection into the queries).  Pairs are interleaved (2i, 2i+1), i < rot/2, rot <= dr, or with
+// split_pairs (i, i + rot/2); angles pos * inv_freq[i].  The cache is [blocks][1][block_size][r + dr].
+// The query heads may lie in rows of their own (`xq`, row stride q_stride; null: in `x` from q_off).
 template <typename T>
 __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* __restrict__ x, long long row_stride, int q_off,
                                                               int c_off, const int* __restrict__ positions,
@@ -103,19 +148,23 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* __restrict
                                                               const float* __restrict__ inv_freq, int rot,
                                                               const int* __restrict__ slots, T* __restrict__ cache,
                                                               T* __restrict__ qa, int nh, int dk, int dr, int r,
-                                                              int block_size, long long num_slots, int* __restrict__ err) {
+                                                              int block_size, long long num_slots, int* __restrict__ err,
+                                                              int split_pairs, const T* __restrict__ xq, long long q_stride) {
   pdl_launch();
   pdl_wait();
   __shared__ float red[32];
   const int n = blockIdx.x;
   const T* row = x + (size_t)n * row_stride;
+  const T* qsrc = xq ? xq + (size_t)n * q_stride : row + q_off;
   const float pos = (float)positions[n];
   // queries: every head's turning part
   T* qrow = qa + (size_t)n * nh * (r + dr);
   for (int idx = threadIdx.x; idx < nh * (dr / 2); idx += blockDim.x) {
     const int h = idx / (dr / 2), i = idx - h * (dr / 2);
-    const T* src = row + q_off + (size_t)h * (dk + dr) + dk;
-    float a = to_float<T>(src[2 * i]), b = to_float<T>(src[2 * i + 1]);
+    const T* src = qsrc + (size_t)h * (dk + dr) + dk;
+    const bool split = split_pairs && 2 * i < rot;
+    const int ia = split ? i : 2 * i, ib = split ? i + rot / 2 : 2 * i + 1;
+    float a = to_float<T>(src[ia]), b = to_float<T>(src[ib]);
     if (2 * i < rot) {
       float sn, cs;
       sincosf(pos * inv_freq[i], &sn, &cs);
@@ -125,8 +174,8 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* __restrict
       b = yb;
     }
     T* dst = qrow + (size_t)h * (r + dr) + r;
-    dst[2 * i] = from_float<T>(a);
-    dst[2 * i + 1] = from_float<T>(b);
+    dst[ia] = from_float<T>(a);
+    dst[ib] = from_float<T>(b);
   }
   const long long slot = slots ? slots[n] : -1;  // uniform over the CTA
   if (slot < 0) return;
@@ -145,7 +194,9 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* __restrict
   T* dst = cache + (size_t)slot * (r + dr);  // one key head: a slot is a row
   for (int j = threadIdx.x; j < r; j += blockDim.x) dst[j] = from_float<T>(to_float<T>(lat[j]) * inv * c_w[j]);
   for (int i = threadIdx.x; i < dr / 2; i += blockDim.x) {
-    float a = to_float<T>(lat[r + 2 * i]), b = to_float<T>(lat[r + 2 * i + 1]);
+    const bool split = split_pairs && 2 * i < rot;
+    const int ia = split ? i : 2 * i, ib = split ? i + rot / 2 : 2 * i + 1;
+    float a = to_float<T>(lat[r + ia]), b = to_float<T>(lat[r + ib]);
     if (2 * i < rot) {
       float sn, cs;
       sincosf(pos * inv_freq[i], &sn, &cs);
@@ -154,8 +205,8 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const T* __restrict
       a = ya;
       b = yb;
     }
-    dst[r + 2 * i] = from_float<T>(a);
-    dst[r + 2 * i + 1] = from_float<T>(b);
+    dst[r + ia] = from_float<T>(a);
+    dst[r + ib] = from_float<T>(b);
   }
 }
 
@@ -195,24 +246,33 @@ inline unsigned grid_for(long long total, int threads) {
                                         const float* k_w, float eps, const float* inv_freq, int rot,                 \
                                         const int* slots, void* kcache, void* vcache, int n_tokens, int nh, int nkv, \
                                         int dk, int dv, int block_size, long long num_slots, int* err,               \
+                                        int split_pairs, void* v_keep, const void* v_first, const float* v_lambda,   \
                                         cudaStream_t st) {                                                           \
     if (n_tokens <= 0) return 0;                                                                                     \
     if (dk <= 0 || (dk & 1) || rot < 0 || rot > dk || (rot & 1)) return (int)cudaErrorInvalidValue;                  \
+    if (v_first && !v_lambda) return (int)cudaErrorInvalidValue;                                                     \
     const long long units = (long long)n_tokens * (nh + 2 * nkv);                                                    \
     return launch(head_norm_cache_kernel<T>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, st, (T*)qkv,           \
                   row_stride, positions, q_w, k_w, eps, inv_freq, rot, slots, (T*)kcache, (T*)vcache, n_tokens, nh,  \
-                  nkv, dk, dv, block_size, num_slots, err);                                                          \
+                  nkv, dk, dv, block_size, num_slots, err, split_pairs, (T*)v_keep, (const T*)v_first, v_lambda);    \
+  }                                                                                                                  \
+  KVF_API int kvf_row_rmsnorm_##SUF(const void* x, long long x_stride, const float* w, float eps, long long n_rows,  \
+                                    int r, void* out, long long out_stride, cudaStream_t st) {                       \
+    if (n_rows <= 0) return 0;                                                                                       \
+    if (r <= 0 || !w) return (int)cudaErrorInvalidValue;                                                             \
+    return launch(row_rmsnorm_kernel<T>, dim3((unsigned)((n_rows + 3) / 4)), dim3(128), 0, st, (const T*)x,          \
+                  x_stride, w, eps, n_rows, r, (T*)out, out_stride);                                                 \
   }                                                                                                                  \
   KVF_API int kvf_latent_prepare_##SUF(const void* x, long long row_stride, int q_off, int c_off,                    \
                                        const int* positions, const float* c_w, float eps, const float* inv_freq,     \
                                        int rot, const int* slots, void* cache, void* qa, int n_tokens, int nh,       \
                                        int dk, int dr, int r, int block_size, long long num_slots, int* err,         \
-                                       cudaStream_t st) {                                                            \
+                                       int split_pairs, const void* xq, long long q_stride, cudaStream_t st) {       \
     if (n_tokens <= 0) return 0;                                                                                     \
     if (r <= 0 || dr < 0 || (dr & 1) || rot < 0 || rot > dr || (rot & 1)) return (int)cudaErrorInvalidValue;         \
     return launch(latent_prepare_kernel<T>, dim3(n_tokens), dim3(128), 0, st, (const T*)x, row_stride, q_off,        \
                   c_off, positions, c_w, eps, inv_freq, rot, slots, (T*)cache, (T*)qa, nh, dk, dr, r, block_size,    \
-                  num_slots, err);                                                                                   \
+                  num_slots, err, split_pairs, (const T*)xq, q_stride);                                              \
   }                                                                                                                  \
   KVF_API int kvf_head_gate_##SUF(void* y, const void* g, long long g_stride, long long n_tokens, int nh, int dv,    \
                                   cudaStream_t st) {                                                                 \

@@ -1,0 +1,234 @@
+// Retention: linear attention with one fixed decay a head, no softmax and no denominator.
+//
+//   S_t = a_h S_(t-1) + k_t v_t^T        (S: [dk][dv] floats per head, in the request's state slot)
+//   o_t = S_t^T q_t
+//
+// q and k turn with the position on their first `rot` dims (pairs (i, i + rot/2), or (2i, 2i+1)); k is then
+// multiplied by k_scale.  Everything from the rotation on is float whatever the storage type T of the projections.
+//
+//   prepare : a warp per (token, head of q, k or v): rotation, scaling, widening to float.  Nothing here depends
+//             on the state, so it runs over all tokens at once.
+//   walk    : a CTA owns (sequence, head, tile of CT value columns) and walks the sequence's tokens in order.  A
+//             column's dk rows are spread over KS neighbouring lanes, R rows each in registers (row i*KS + s for lane
+//             s).  Per token a lane makes  S <- a S + k v  and its part of  S^T q  in one pass; the KS parts are
+//             added in a fixed tree.  Chunks of TC tokens come in through a cp.async double buffer; the state
+//             tile passes through shared memory so that global memory sees whole rows.
+//
+// The state after a token is the same bits however the sequence was cut into steps (the walk is token by token,
+// and every sum has an order fixed by dk alone), so a token's output does not depend on the cut, the batch or
+// the slot.  A sequence without rows, or with a slot below zero (padding), touches nothing.
+#include "common.cuh"
+
+using namespace kvf;
+
+namespace {
+
+constexpr int TC = 16;  // tokens per chunk of the walk
+
+template <typename T>
+__global__ void __launch_bounds__(128) retention_prepare_kernel(const T* __restrict__ x, long long x_stride, int q_off, int k_off,
+                                                                 int v_off, const int* __restrict__ positions,
+                                                                 const float* __restrict__ inv_freq, int rot, int split_pairs,
+                                                                 float k_scale, long long n_tokens, int H, int dk, int dv,
+                                                                 float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vn) {
+  pdl_launch();
+  pdl_wait();
+  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit >= n_tokens * 3 * H) return;
+  const long long n = unit / (3 * H);
+  const int u = (int)(unit - n * 3 * H), kind = u / H, h = u - kind * H;
+  const int lane = threadIdx.x & 31;
+  const T* row = x + (size_t)n * x_stride;
+  if (kind == 2) {
+    const T* src = row + v_off + (size_t)h * dv;
+    float* dst = vn + ((size_t)n * H + h) * dv;
+    for (int j = lane; j < dv; j += 32) dst[j] = to_float<T>(src[j]);
+    return;
+  }
+  const T* src = row + (kind == 0 ? q_off : k_off) + (size_t)h * dk;
+  float* dst = (kind == 0 ? qn : kn) + ((size_t)n * H + h) * dk;
+  const float mul = kind == 0 ? 1.f : k_scale;
+  const float pos = (float)positions[n];
+  for (int i = lane; i < dk / 2; i += 32) {
+    const bool turns = 2 * i < rot;
+    const int ia = (turns && split_pairs) ? i : 2 * i, ib = (turns && split_pairs) ? i + rot / 2 : 2 * i + 1;
+    float a = to_float<T>(src[ia]), b = to_float<T>(src[ib]);
+    if (turns) {
+      float sn, cs;
+      sincosf(pos * inv_freq[i], &sn, &cs);
+      float ya, yb;
+      rotate_pair(a, b, cs, sn, ya, yb);
+      a = ya;
+      b = yb;
+    }
+    dst[ia] = a * mul;
+    dst[ib] = b * mul;
+  }
+  if ((dk & 1) && lane == 0) dst[dk - 1] = to_float<T>(src[dk - 1]) * mul;
+}
+
+__device__ __forceinline__ void cp_async(float* dst, const float* src, bool wide) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  if (wide)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src));
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src));
+}
+
+// R rows a lane; blockDim.x = KS * CT (a multiple of 32, at most 128); KS a power of two, at most 32.
+template <int R>
+__global__ void __launch_bounds__(128) retention_walk_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
+                                                              const float* __restrict__ vn, const float* __restrict__ decay,
+                                                              float* __restrict__ state, long long state_stride,
+                                                              float* __restrict__ out, long long out_stride,
+                                                              const int* __restrict__ qsl, const int* __restrict__ state_slots,
+                                                              int H, int dk, int dv, int KS, int CT) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ __align__(16) float sm[];
+  const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * CT;
+  const int q_begin = qsl[b], q_len = qsl[b + 1] - q_begin;
+  const int slot = state_slots[b];
+  if (q_len <= 0 || slot < 0) return;
+  const int dkp = KS * R, tid = threadIdx.x, nthreads = blockDim.x;
+  const int s = tid & (KS - 1), col = tid / KS;
+  const int ncol = min(CT, dv - c0);
+  const int lds = CT + 1;
+  float* St = sm;                       // [dkp][CT + 1]: the state tile on its way in and out
+  const int st_floats = (dkp * lds + 3) & ~3;
+  const int stage = TC * (2 * dkp + CT);  // q [TC][dkp], k [TC][dkp], v [TC][CT]
+  float* buf = sm + st_floats;
+  const float a = decay[h];
+
+  float* sbase = state + (size_t)slot * state_stride + (size_t)h * dk * dv + c0;
+  for (int idx = tid; idx < dkp * CT; idx += nthreads) {
+    const int r = idx / CT, c = idx - r * CT;
+    St[r * lds + c] = (r < dk && c < ncol) ? sbase[(size_t)r * dv + c] : 0.f;
+  }
+  // what no copy ever writes is zero for good: rows of q and k beyond dk, value columns beyond the tile's
+  for (int idx = tid; idx < 2 * stage; idx += nthreads) buf[idx] = 0.f;
+  __syncthreads();
+  float S[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) S[i] = St[(i * KS + s) * lds + col];
+
+  const bool wide_qk = (dk & 3) == 0, wide_v = (dv & 3) == 0 && (c0 & 3) == 0 && (ncol & 3) == 0;
+  auto issue = [&](int chunk) {
+    float* bq = buf + (chunk & 1) * stage;
+    float* bk = bq + TC * dkp;
+    float* bv = bk + TC * dkp;
+    const int t0 = chunk * TC, nt = min(TC, q_len - t0);
+    const int per = wide_qk ? dk / 4 : dk;
+    for (int idx = tid; idx < nt * per; idx += nthreads) {
+      const int t = idx / per, j = (idx - t * per) * (wide_qk ? 4 : 1);
+      const size_t g = ((size_t)(q_begin + t0 + t) * H + h) * dk + j;
+      cp_async(bq + t * dkp + j, qn + g, wide_qk);
+      cp_async(bk + t * dkp + j, kn + g, wide_qk);
+    }
+    const int perv = wide_v ? ncol / 4 : ncol;
+    for (int idx = tid; idx < nt * perv; idx += nthreads) {
+      const int t = idx / perv, j = (idx - t * perv) * (wide_v ? 4 : 1);
+      cp_async(bv + t * CT + j, vn + ((size_t)(q_begin + t0 + t) * H + h) * dv + c0 + j, wide_v);
+    }
+  };
+
+  const int nchunks = (q_len + TC - 1) / TC;
+  issue(0);
+  asm volatile("cp.async.commit_group;\n" ::);
+  for (int c = 0; c < nchunks; ++c) {
+    if (c + 1 < nchunks) issue(c + 1);
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 1;\n" ::);
+    __syncthreads();
+    const float* bq = buf + (c & 1) * stage;
+    const float* bk = bq + TC * dkp;
+    const float* bv = bk + TC * dkp;
+    const int t0 = c * TC, nt = min(TC, q_len - t0);
+    for (int t = 0; t < nt; ++t) {
+      const float* q = bq + t * dkp + s;
+      const float* k = bk + t * dkp + s;
+      const float vv = bv[t * CT + col];
+      float p = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        S[i] = fmaf(a, S[i], __fmul_rn(k[i * KS], vv));
+        p = fmaf(S[i], q[i * KS], p);
+      }
+      for (int o = KS >> 1; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+      if (s == 0 && col < ncol) out[(size_t)(q_begin + t0 + t) * out_stride + (size_t)h * dv + c0 + col] = p;
+    }
+    __syncthreads();  // the chunk is used up: the copy after next may overwrite it
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
+#pragma unroll
+  for (int i = 0; i < R; ++i) St[(i * KS + s) * lds + col] = S[i];
+  __syncthreads();
+  for (int idx = tid; idx < dk * ncol; idx += nthreads) {
+    const int r = idx / ncol, c = idx - r * ncol;
+    sbase[(size_t)r * dv + c] = St[r * lds + c];
+  }
+}
+
+inline int pow2_at_least(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+template <int R>
+int launch_walk(const float* qn, const float* kn, const float* vn, const float* decay, float* state, long long state_stride, float* out,
+                long long out_stride, const int* qsl, const int* state_slots, int B, int H, int dk, int dv, cudaStream_t st) {
+  int KS = pow2_at_least((dk + R - 1) / R);
+  if (KS > 32) return (int)cudaErrorInvalidValue;
+  int CT = 128 / KS;
+  const int cols = pow2_at_least(dv);
+  if (CT > cols) CT = cols;
+  if (CT * KS < 32) CT = 32 / KS;
+  // few (sequence, head) pairs: narrower tiles, so that there are CTAs for every SM
+  while (CT * KS > 32 && CT > 4 && (long long)B * H * ((dv + CT - 1) / CT) < 2 * 148) CT >>= 1;
+  const int dkp = KS * R;
+  const size_t smem = (size_t)(((dkp * (CT + 1) + 3) & ~3) + 2 * TC * (2 * dkp + CT)) * sizeof(float);
+  auto kern = retention_walk_kernel<R>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return launch(kern, dim3((dv + CT - 1) / CT, H, B), dim3(KS * CT), smem, st, qn, kn, vn, decay, state, state_stride, out, out_stride,
+                qsl, state_slots, H, dk, dv, KS, CT);
+}
+
+}  // namespace
+
+// x: rows of the projections (q heads from q_off, k heads from k_off, v heads from v_off; H heads each of dk, dk, dv).
+// qn, kn [N][H*dk] and vn [N][H*dv]: float scratch.  state: float, slot i at state + i * state_stride, [H][dk][dv].
+// out: float [N][H*dv] (row stride out_stride).  decay: float [H].  Two launches.
+#define KVF_RETENTION_API(SUF, T)                                                                                       \
+  KVF_API int kvf_retention_##SUF(const void* x, long long x_stride, int q_off, int k_off, int v_off,                   \
+                                  const int* positions, const float* inv_freq, int rot, int split_pairs,                \
+                                  float k_scale, const float* decay, float* state, long long state_stride, float* out,  \
+                                  long long out_stride, const int* qsl, const int* state_slots, int B, long long N,     \
+                                  int H, int dk, int dv, float* qn, float* kn, float* vn, cudaStream_t st) {            \
+    if (B <= 0 || N <= 0) return 0;                                                                                     \
+    if (H <= 0 || dk <= 0 || dk > 512 || dv <= 0 || rot < 0 || rot > dk || (rot & 1) || (unsigned)B > 65535u ||         \
+        (unsigned)H > 65535u)                                                                                           \
+      return (int)cudaErrorInvalidValue;                                                                                \
+    const long long units = N * 3 * H;                                                                                  \
+    int rc = launch(retention_prepare_kernel<T>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, st, (const T*)x,      \
+                    x_stride, q_off, k_off, v_off, positions, inv_freq, rot, split_pairs, k_scale, N, H, dk, dv, qn,    \
+                    kn, vn);                                                                                            \
+    if (rc) return rc;                                                                                                  \
+    if (dk <= 16)                                                                                                       \
+      return launch_walk<4>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,    \
+                            st);                                                                                        \
+    if (dk <= 32)                                                                                                       \
+      return launch_walk<8>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,    \
+                            st);                                                                                        \
+    if (dk <= 64)                                                                                                       \
+      return launch_walk<16>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,   \
+                             st);                                                                                       \
+    return launch_walk<32>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,     \
+                           st);                                                                                         \
+  }
+
+KVF_RETENTION_API(f32, float)
+KVF_RETENTION_API(bf16, bf16)

@@ -45,6 +45,8 @@ LIBRARIES: dict[str, tuple[list[str], list[str]]] = {
     # layers whose sublayer results are gated and normed before they join the residual stream, heads that are
     # rotated and then normed, attention whose heads talk before the softmax; a library of its own for the same reason
     "gated": (["gated_ops.cu", "attention_talking_f32.cu", "attention_talking_bf16.cu", "attention_talking_mma.cu"], []),
+    # a recurrent mixer with a fixed decay a head and a norm without statistics; a library of its own for the same reason
+    "decay": (["retention.cu", "tanh_norm.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

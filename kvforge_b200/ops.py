@@ -24,7 +24,7 @@ _SIGNATURES = {
     "kvf_rope_cache_{s}": "ppilppppppiiiiiilpp",
     "kvf_silu_mul_{s}": "ppliip",
     "kvf_cast_from_float_{s}": "pplp",
-    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiiifiiiippiipip",
+    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiiifiiiippiipifpp",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_mma_biased_bf16": "pppppppiiiiiiiiifiipip",
     "kvf_latent_attention_bf16": "ppppppiiiiiiiiifiiiippp",
@@ -50,17 +50,18 @@ _SIGNATURES = {
     "kvf_softcap_f32": "plfp",
     "kvf_mixers_set_pdl": "i",
     # library "routed"
-    "kvf_head_norm_cache_{s}": "plpppfpipppiiiiiilpp",
-    "kvf_latent_prepare_{s}": "pliippfpipppiiiiiilpp",
+    "kvf_head_norm_cache_{s}": "plpppfpipppiiiiiilpipppp",
+    "kvf_latent_prepare_{s}": "pliippfpipppiiiiiilpiplp",
+    "kvf_row_rmsnorm_{s}": "plpfliplp",
     "kvf_head_gate_{s}": "pplliip",
     "kvf_add_row_f32": "pplip",
-    "kvf_moe_route_{s}": "plppiiiiiifippp",
-    "kvf_moe_experts_{s}": "plppppiiiiippppppip",
+    "kvf_moe_route_{s}": "plppiiiiiifipppp",
+    "kvf_moe_experts_{s}": "plppppiiiiippppppifffp",
     "kvf_moe_max_tiles": "ii",
     "kvf_moe_sort": "piiipppp",
     "kvf_moe_gather_bf16": "plpiiipp",
     "kvf_moe_combine": "pppiiip",
-    "kvf_gemm_grouped_tcgen05_bf16": "pppiiiiiiipppipp",
+    "kvf_gemm_grouped_tcgen05_bf16": "pppiiiiiiipppipfffp",
     "kvf_routed_set_pdl": "i",
     # library "gated"
     "kvf_norm_step_{s}": "pppplliplppppliiiifp",
@@ -70,6 +71,10 @@ _SIGNATURES = {
     "kvf_talking_attention_mma_bf16": "pppppppppiiiiiiiiiifiiiippp",
     "kvf_talking_mma_ok": "iiiiii",
     "kvf_gated_set_pdl": "i",
+    # library "decay"
+    "kvf_retention_{s}": "pliiippiifpplplppiliiipppp",
+    "kvf_tanh_norm_{s}": "pppilfppppplip",
+    "kvf_decay_set_pdl": "i",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 
@@ -149,7 +154,7 @@ def set_pdl(enabled: bool) -> None:
 
 
 # every shared library has a flag of its own; it follows the core's once the library is loaded
-_PDL_SETTERS = {"mixers": "kvf_mixers_set_pdl", "routed": "kvf_routed_set_pdl", "gated": "kvf_gated_set_pdl"}
+_PDL_SETTERS = {"mixers": "kvf_mixers_set_pdl", "routed": "kvf_routed_set_pdl", "gated": "kvf_gated_set_pdl", "decay": "kvf_decay_set_pdl"}
 _library_pdl: dict[str, bool] = {}
 
 
@@ -546,6 +551,8 @@ def paged_attention(
     dv: int | None = None,
     keep_first: int = 0,
     bias: DistanceBias | None = None,
+    softcap: float = 0.0,
+    sinks: torch.Tensor | None = None,
 ) -> None:
     """Paged GQA attention of a flat batch (the contract is at the top of
     ``csrc/attention_generic.cu``).
@@ -554,7 +561,9 @@ def paged_attention(
     ``[num_blocks, nkv, block_size, dv]`` and ``out`` ``[N, nh*dv]``); only the FP32-pipe kernel
     takes such a shape.  So it is with ``vcache is kcache`` (a value is the first ``dv`` numbers of
     its key), with ``keep_first`` (under a window, the first keys of every sequence stay visible at
-    any distance) and with ``bias`` (added to the scaled scores, by distance and head).
+    any distance), with ``bias`` (added to the scaled scores, by distance and head), with ``softcap``
+    (``c > 0``: a scaled score ``s`` becomes ``c * tanh(s / c)``) and with ``sinks`` (float ``[nh]``: ``exp(sinks[h])``
+    joins the softmax's denominator of head ``h``; it has no key and no value).
 
     ``q``: rows of ``q_stride`` elements whose first ``nh*d`` are the query heads; ``out``:
     ``[N, nh*d]``.  With ``scratch`` (and every sequence holding one query) the decode form
@@ -573,16 +582,19 @@ def paged_attention(
     context, over all pairs, are at most this many (``attention_wave_target``).
     """
     s = _suffix(q.dtype)
-    special = vcache is kcache or keep_first > 0 or bias is not None or d > 256 or (dv or d) > 256
+    capped = float(softcap) > 0.0 or sinks is not None  # the FP32-pipe kernel's alone
+    if float(softcap) < 0.0:
+        raise ValueError("paged_attention: softcap must be positive (0: none)")
+    special = vcache is kcache or keep_first > 0 or bias is not None or d > 256 or (dv or d) > 256 or capped
     # kept first keys and a bias alone, on heads of 64 or 128 in bfloat16 with many queries: the tile form of the mma.sync kernel
     biased_mma = (
-        special and vcache is not kcache and (dv or d) == d and kernel == "auto"
+        special and not capped and vcache is not kcache and (dv or d) == d and kernel == "auto"
         and mma_attention_supported(q.dtype, nh, nkv, d, scratch is not None) and (q_stride or q.shape[-1]) % 2 == 0 and out.shape[-1] % 2 == 0
         and (scratch is None or len(scratch) > 2)
     )  # fmt: skip
     if special and not biased_mma:
         if kernel not in ("auto", "generic"):
-            raise ValueError("only the FP32-pipe attention kernel takes kept first keys, a distance bias, values inside keys or heads wider than 256")
+            raise ValueError("only the FP32-pipe attention kernel takes kept first keys, a distance bias, capped scores, sinks, values inside keys or heads wider than 256")
         kernel = "generic"
     check_head_dim(d, MAX_KEY_DIM if special and not biased_mma else 256)
     _need(q, None, "q")
@@ -615,6 +627,10 @@ def paged_attention(
         bias_args = (_ptr(bias.by_distance), bias.bucket.numel() - 1)
     if keep_first < 0:
         raise ValueError("paged_attention: keep_first is a count of keys")
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
+        if sinks.numel() != nh:
+            raise ValueError("paged_attention: one sink per head")
     if dv != d:
         if kernel not in ("auto", "generic"):
             raise ValueError("only the FP32-pipe attention kernel takes a value size of its own")
@@ -730,7 +746,7 @@ def paged_attention(
         _fn(name)(
             _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
             num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, *((dv,) if not use_mma else ()), block_size, float(scale),
-            int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), *(() if use_mma else (int(keep_first), v_stride, *bias_args)), _stream(),
+            int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), *(() if use_mma else (int(keep_first), v_stride, *bias_args, float(softcap), _ptr(sinks))), _stream(),
         ),
         name,
         2 if scratch is not None else 1,
@@ -1402,14 +1418,18 @@ def add_row(resid: torch.Tensor, row: torch.Tensor) -> None:
 def head_norm_cache(
     qkv: torch.Tensor, positions: torch.Tensor, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
     inv_freq: torch.Tensor | None, slots: torch.Tensor | None, kcache: torch.Tensor | None, vcache: torch.Tensor | None,
-    nh: int, nkv: int, dk: int, dv: int, block_size: int, err: torch.Tensor | None = None,
+    nh: int, nkv: int, dk: int, dv: int, block_size: int, err: torch.Tensor | None = None, interleaved: bool = True,
+    v_keep: torch.Tensor | None = None, v_first: torch.Tensor | None = None, v_lambda: torch.Tensor | None = None,
 ) -> None:  # fmt: skip
     """What follows the q/k/v product of an attention layer whose queries and keys are normed per
     head: rows of ``qkv`` hold ``nh`` query heads and ``nkv`` key heads of ``dk`` and ``nkv`` value heads
     of ``dv``.  Query and key heads become ``x / sqrt(mean(x^2) + eps) * weight`` (``weight`` float
     ``[dk]``, shared by the heads; ``None``: left as they are), then their first ``2*len(inv_freq)``
-    dims turn in interleaved pairs (``None``: no rotation); queries in place, keys and values to
-    ``slots`` of ``kcache [blocks, nkv, block_size, dk]`` / ``vcache [..., dv]``."""
+    dims turn in interleaved pairs ``(2i, 2i+1)`` or, with ``interleaved=False``, in split pairs ``(i, i + rot/2)``
+    (``None``: no rotation); queries in place, keys and values to ``slots`` of
+    ``kcache [blocks, nkv, block_size, dk]`` / ``vcache [..., dv]``.  ``v_keep [N, nkv*dv]``: the values as projected
+    are copied there as well (for later layers of the step).  ``v_first [N, nkv*dv]`` with ``v_lambda`` (a float
+    scalar on the device): the cached value is ``(1 - lambda) v + lambda v_first``."""
     s = _suffix(qkv.dtype)
     _rows2d(qkv, None, "qkv")
     n = qkv.shape[0]
@@ -1435,11 +1455,21 @@ def head_norm_cache(
         if tuple(kcache.shape[1:]) != (nkv, block_size, dk) or tuple(vcache.shape) != (*kcache.shape[:3], dv):
             raise ValueError("head_norm_cache: cache shapes must be [num_blocks, nkv, block_size, dk] and [..., dv]")
         num_slots = kcache.shape[0] * block_size
+    for t, what in ((v_keep, "v_keep"), (v_first, "v_first")):
+        if t is not None:
+            _need(t, qkv.dtype, what)
+            if tuple(t.shape) != (n, nkv * dv):
+                raise ValueError(f"head_norm_cache: {what} must be [N, nkv*dv]")
+    if v_first is not None:
+        _need(v_lambda, torch.float32, "v_lambda")
+        if v_lambda.numel() != 1:
+            raise ValueError("head_norm_cache: v_lambda is one number")
     name = f"kvf_head_norm_cache_{s}"
     _check(
         _fn(name, ROUTED_LIB)(
             _ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq) if rot else None, rot,
-            _ptr(slots), _ptr(kcache), _ptr(vcache), n, nh, nkv if slots is not None else 0, dk, dv, block_size, num_slots, _ptr(err), _stream(),
+            _ptr(slots), _ptr(kcache), _ptr(vcache), n, nh, nkv if slots is not None else 0, dk, dv, block_size, num_slots, _ptr(err),
+            0 if interleaved else 1, _ptr(v_keep), _ptr(v_first), _ptr(v_lambda) if v_first is not None else None, _stream(),
         ),
         name,
     )  # fmt: skip
@@ -1448,14 +1478,16 @@ def head_norm_cache(
 def latent_prepare(
     x: torch.Tensor, q_off: int, c_off: int, positions: torch.Tensor, c_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor | None,
     slots: torch.Tensor, cache: torch.Tensor, qa: torch.Tensor, nh: int, dk: int, dr: int, rank: int, block_size: int,
-    err: torch.Tensor | None = None,
+    err: torch.Tensor | None = None, interleaved: bool = True, q: torch.Tensor | None = None,
 ) -> None:  # fmt: skip
     """For an attention layer whose keys and values come from one latent per token.  Rows of ``x`` hold,
     from column ``q_off``, ``nh`` query heads of ``dk + dr`` and, from ``c_off``, ``rank`` latent numbers and
     ``dr`` numbers of a key part shared by all heads.  The latent, RMS-normed with ``c_weight``, and the
     shared key part, turned with the position, go to ``slots`` of ``cache [blocks, 1, block_size, rank + dr]``;
     every query head's last ``dr`` numbers, turned, go to columns ``rank .. rank + dr`` of its head in
-    ``qa [N, nh * (rank + dr)]``.  Pairs are interleaved; ``inv_freq`` float ``[rot/2]``, ``rot <= dr``."""
+    ``qa [N, nh * (rank + dr)]``.  Pairs are interleaved ``(2i, 2i+1)`` or, with ``interleaved=False``, split
+    ``(i, i + rot/2)``; ``inv_freq`` float ``[rot/2]``, ``rot <= dr``.  ``q [N, nh*(dk+dr)]``: the query heads lie in
+    rows of their own (``q_off`` is then ignored)."""
     s = _suffix(x.dtype)
     _rows2d(x, None, "x")
     _need(qa, x.dtype, "qa")
@@ -1464,7 +1496,12 @@ def latent_prepare(
     _need(slots, torch.int32, "slots")
     _need(c_weight, torch.float32, "latent norm weight")
     n = x.shape[0]
-    if q_off + nh * (dk + dr) > x.shape[1] or c_off + rank + dr > x.shape[1] or c_weight.numel() != rank or dr % 2:
+    if q is not None:
+        _rows2d(q, x.dtype, "q")
+        if tuple(q.shape) != (n, nh * (dk + dr)):
+            raise ValueError("latent_prepare: q must be [N, nh*(dk+dr)]")
+        q_off = 0
+    if (q is None and q_off + nh * (dk + dr) > x.shape[1]) or c_off + rank + dr > x.shape[1] or c_weight.numel() != rank or dr % 2:
         raise ValueError("latent_prepare: the columns do not fit the rows")
     if tuple(qa.shape) != (n, nh * (rank + dr)) or tuple(cache.shape[1:]) != (1, block_size, rank + dr):
         raise ValueError("latent_prepare: qa must be [N, nh*(rank+dr)] and the cache [blocks, 1, block_size, rank+dr]")
@@ -1478,10 +1515,24 @@ def latent_prepare(
     _check(
         _fn(name, ROUTED_LIB)(
             _ptr(x), x.stride(0), int(q_off), int(c_off), _ptr(positions), _ptr(c_weight), float(eps), _ptr(inv_freq) if rot else None, rot,
-            _ptr(slots), _ptr(cache), _ptr(qa), n, nh, dk, dr, rank, block_size, cache.shape[0] * block_size, _ptr(err), _stream(),
+            _ptr(slots), _ptr(cache), _ptr(qa), n, nh, dk, dr, rank, block_size, cache.shape[0] * block_size, _ptr(err),
+            0 if interleaved else 1, _ptr(q), q.stride(0) if q is not None else 0, _stream(),
         ),
         name,
     )  # fmt: skip
+
+
+def row_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``out[n] = x[n] / sqrt(mean(x[n]^2) + eps) * weight`` in float, rounded once; ``x [N, r]`` may be a column range of
+    wider rows, ``out [N, r]`` likewise, ``weight`` float ``[r]``."""
+    s = _suffix(x.dtype)
+    _rows2d(x, None, "x")
+    _rows2d(out, x.dtype, "out")
+    _need(weight, torch.float32, "norm weight")
+    if out.shape != x.shape or weight.numel() != x.shape[1]:
+        raise ValueError("row_rmsnorm: shapes do not agree")
+    name = f"kvf_row_rmsnorm_{s}"
+    _check(_fn(name, ROUTED_LIB)(_ptr(x), x.stride(0), _ptr(weight), float(eps), x.shape[0], x.shape[1], _ptr(out), out.stride(0), _stream()), name)
 
 
 def head_gate(y: torch.Tensor, gate: torch.Tensor, nh: int, dv: int) -> None:
@@ -1503,14 +1554,17 @@ def moe_max_tiles(n_pairs: int, num_experts: int) -> int:
 
 def moe_route(
     x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int, keep: int, norm_eps: float,
-    ids: torch.Tensor, weights: torch.Tensor, softmax: bool = False, normalize: bool = True,
+    ids: torch.Tensor, weights: torch.Tensor, softmax: bool = False, normalize: bool = True, bias: torch.Tensor | None = None,
+    chosen_softmax: bool = False,
 ) -> None:  # fmt: skip
     """Per token of ``x [N, W]``: logits ``router [E, W] x`` in float, scores ``s = sigmoid(z)``; the ``top``
     experts with the largest ``s + correction`` among the best ``keep`` of ``groups`` equal groups of
     neighbouring experts (a group's rank: the sum of the top two ``s + correction`` among its members) are chosen
     (``ids`` int32 ``[N, top]``); their weights are their ``s`` over the sum of those (+ ``norm_eps``)
     (``weights`` float ``[N, top]``).  ``softmax``: the scores are ``softmax(z)`` over all experts instead;
-    ``normalize=False``: the weights are the chosen scores as they are."""
+    ``normalize=False``: the weights are the chosen scores as they are.  ``bias`` (float ``[E]``) is added to the
+    logits.  ``chosen_softmax``: the logits themselves rank the experts and the weights are a softmax over the chosen
+    logits alone (``softmax``, ``normalize`` and ``norm_eps`` then play no part)."""
     s = _suffix(x.dtype)
     _rows2d(x, None, "x")
     _need(router, torch.float32, "router")
@@ -1522,18 +1576,36 @@ def moe_route(
         _need(correction, torch.float32, "correction")
         if correction.numel() != e:
             raise ValueError("moe_route: one correction per expert")
+    if bias is not None:
+        _need(bias, torch.float32, "router bias")
+        if bias.numel() != e:
+            raise ValueError("moe_route: one bias per expert")
     _need(ids, torch.int32, "ids")
     _need(weights, torch.float32, "weights")
     if tuple(ids.shape) != (n, top) or tuple(weights.shape) != (n, top):
         raise ValueError("moe_route: ids and weights must be [N, top]")
+    flags = 4 if chosen_softmax else (1 if softmax else 0) | (0 if normalize else 2)
     name = f"kvf_moe_route_{s}"
     _check(
-        _fn(name, ROUTED_LIB)(_ptr(x), x.stride(0), _ptr(router), _ptr(correction), n, w, e, int(top), int(groups), int(keep), float(norm_eps), (1 if softmax else 0) | (0 if normalize else 2), _ptr(ids), _ptr(weights), _stream()),
+        _fn(name, ROUTED_LIB)(_ptr(x), x.stride(0), _ptr(router), _ptr(correction), n, w, e, int(top), int(groups), int(keep), float(norm_eps), flags, _ptr(ids), _ptr(weights), _ptr(bias), _stream()),
         name,
     )
 
 
-EXPERT_ACTIVATIONS = {"gelu": 0, "relu2": 1}  # what the experts' kernels apply between their two products
+# what the experts' kernels apply between their two products; "gated": the first matrix holds gate and up rows in
+# alternating blocks of GATE_UP_BLOCK (``interleave_gate_up``) and the two are joined (``GatedActivation``)
+EXPERT_ACTIVATIONS = {"gelu": 0, "relu2": 1, "gated": 2}
+
+
+@dataclass(frozen=True)
+class GatedActivation:
+    """``g' / (1 + exp(-alpha g')) * (u' + shift)`` with ``g' = min(g, limit)`` and ``u' = clamp(u, -limit, limit)``:
+    the defaults are SwiGLU (``silu(g) * u``)."""
+
+    limit: float = float("inf")
+    alpha: float = 1.0
+    shift: float = 0.0
+
 GROUPED_TILE_ROWS = 128  # rows of a tile of the tensor-memory product
 # from this many rows an expert (on average) the two products of routed experts run on the tcgen05 tensor cores
 GROUPED_TCGEN05_MIN_ROWS = 64
@@ -1541,14 +1613,16 @@ GROUPED_TCGEN05_MIN_ROWS = 64
 
 def moe_experts(
     x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, scratch: dict, resid: torch.Tensor,
-    err: torch.Tensor | None = None, activation: str = "gelu",
+    err: torch.Tensor | None = None, activation: str = "gelu", gated: GatedActivation | None = None,
 ) -> None:  # fmt: skip
     """``resid[n] += sum_k weights[n, k] * w_down[e] act(w_up[e] x[n])`` with ``e = ids[n, k]`` and ``act`` the exact
     GELU (``"gelu"``) or the square of relu (``"relu2"``): the pairs are
     ordered by expert, every expert's rows go through its two products in tiles, and the results are
     summed per token in the order of ``k``.  ``w_up [E, ff, W]``, ``w_down [E, W, ff]``; ``scratch``: ``order``
     int32 ``[N*top]``, ``tiles`` int32 ``[3*max_tiles]``, ``meta`` int32 ``[4]``, ``act [N*top, ff]``, ``y`` float
-    ``[N*top, W]``, and for many bfloat16 rows ``xs [N*top, W]`` (the pairs' rows side by side by expert).  Four
+    ``[N*top, W]``, and for many bfloat16 rows ``xs [N*top, W]`` (the pairs' rows side by side by expert).  With
+    ``activation="gated"`` ``w_up`` is ``[E, 2*ff, W]``, gate and up rows alternating in blocks of 8, and ``gated`` says how
+    they are joined.  Four
     launches, five through the tensor-memory product (``err``: the device flag its bounded waits raise)."""
     s = _suffix(x.dtype)
     if activation not in EXPERT_ACTIVATIONS:
@@ -1559,9 +1633,13 @@ def moe_experts(
     _need(w_down, x.dtype, "w_down")
     _need(resid, torch.float32, "resid")
     n, w = x.shape
-    e, ff = w_up.shape[0], w_up.shape[1]
+    is_gated = activation == "gated"
+    ga = gated or GatedActivation()
+    e, ff = w_up.shape[0], w_up.shape[1] // (2 if is_gated else 1)
     top = ids.shape[1]
-    if tuple(w_up.shape) != (e, ff, w) or tuple(w_down.shape) != (e, w, ff) or tuple(resid.shape) != (n, w):
+    if is_gated and ff % GATE_UP_BLOCK:
+        raise ValueError("moe_experts: gated experts need an inner size that is a multiple of 8")
+    if tuple(w_up.shape) != (e, ff * (2 if is_gated else 1), w) or tuple(w_down.shape) != (e, w, ff) or tuple(resid.shape) != (n, w):
         raise ValueError("moe_experts: shapes do not agree")
     _need(ids, torch.int32, "ids")
     _need(weights, torch.float32, "weights")
@@ -1585,15 +1663,16 @@ def moe_experts(
         _check(_fn("kvf_moe_sort", ROUTED_LIB)(_ptr(ids), pairs, e, GROUPED_TILE_ROWS, _ptr(order), _ptr(tiles), _ptr(meta), st), "kvf_moe_sort")
         _check(_fn("kvf_moe_gather_bf16", ROUTED_LIB)(_ptr(x), x.stride(0), _ptr(order), top, pairs, w, _ptr(xs), st), "kvf_moe_gather_bf16")
         g = _fn("kvf_gemm_grouped_tcgen05_bf16")
-        _check(g(_ptr(xs), _ptr(w_up), _ptr(act), pairs, ff, w, e, w, ff, 1 + act_kind, _ptr(tiles), _ptr(meta), None, row_tiles, _ptr(err), st), "kvf_gemm_grouped_tcgen05_bf16")
-        _check(g(_ptr(act), _ptr(w_down), _ptr(y), pairs, w, ff, e, ff, w, 0, _ptr(tiles), _ptr(meta), _ptr(order), row_tiles, _ptr(err), st), "kvf_gemm_grouped_tcgen05_bf16")
+        fl = (float(ga.limit), float(ga.alpha), float(ga.shift))
+        _check(g(_ptr(xs), _ptr(w_up), _ptr(act), pairs, ff * (2 if is_gated else 1), w, e, w, ff, 1 + act_kind, _ptr(tiles), _ptr(meta), None, row_tiles, _ptr(err), *fl, st), "kvf_gemm_grouped_tcgen05_bf16")
+        _check(g(_ptr(act), _ptr(w_down), _ptr(y), pairs, w, ff, e, ff, w, 0, _ptr(tiles), _ptr(meta), _ptr(order), row_tiles, _ptr(err), *fl, st), "kvf_gemm_grouped_tcgen05_bf16")
         _check(_fn("kvf_moe_combine", ROUTED_LIB)(_ptr(resid), _ptr(y), _ptr(weights), n, w, top, st), "kvf_moe_combine")
         return
     name = f"kvf_moe_experts_{s}"
     _check(
         _fn(name, ROUTED_LIB)(
             _ptr(x), x.stride(0), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), n, w, ff, e, top, _ptr(order), _ptr(tiles), _ptr(meta),
-            _ptr(act), _ptr(y), _ptr(resid), act_kind, _stream(),
+            _ptr(act), _ptr(y), _ptr(resid), act_kind, float(ga.limit), float(ga.alpha), float(ga.shift), _stream(),
         ),
         name,
         4,
@@ -1832,4 +1911,131 @@ def talking_attention(
         ),
         name,
         2 if scratch is not None else 1,
+    )  # fmt: skip
+
+
+# ------------------------------------------------------------------ library "decay"
+# a norm without statistics, and a recurrent mixer with one fixed decay a head
+
+DECAY_LIB = "decay"
+
+
+@dataclass
+class Scaled:
+    """A sublayer's result that joins the residual stream multiplied by ``mult``: ``what`` is a tensor in the
+    storage type, ``Partials`` or ``None``; the norm that follows adds ``mult * what`` in 32-bit."""
+
+    what: object
+    mult: float
+
+
+def tanh_norm(
+    resid: torch.Tensor, delta: torch.Tensor | Partials | Scaled | None, alpha: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+    out: torch.Tensor | None, rows: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """``v = resid + mult * delta`` (written back into ``resid`` unless ``rows`` is given), ``out = T(tanh(alpha * v) *
+    weight + bias)``: a norm that computes no mean and no variance.  ``alpha`` is a float scalar on the device,
+    ``weight`` and ``bias`` float ``[H]``.  ``delta``: a tensor in the storage type, the ``Partials`` of a split product, or
+    either inside ``Scaled`` (``mult`` is 1 otherwise).  With ``rows`` (int32 ``[R]``) row ``r`` of ``out`` comes from row
+    ``rows[r]``.  ``out=None``: only the sum is made."""
+    _need(resid, torch.float32, "resid")
+    for t, what in ((alpha, "alpha"), (weight, "norm weight"), (bias, "norm bias")):
+        _need(t, torch.float32, what)
+    h = resid.shape[-1]
+    if alpha.numel() != 1 or weight.numel() != h or bias.numel() != h:
+        raise ValueError("tanh_norm: alpha is one number, weight and bias are as wide as the stream")
+    mult = 1.0
+    if isinstance(delta, Scaled):
+        delta, mult = delta.what, float(delta.mult)
+    if delta is ADDED:
+        delta = None
+    dptr, pptr, nsplit, stride = None, None, 0, 0
+    dtype = out.dtype if out is not None else None
+    if isinstance(delta, Partials):
+        _need(delta.t, torch.float32, "partials", contiguous=False)
+        if delta.t.shape[-1] != h or delta.t.stride(1) != h or delta.t.stride(2) != 1:
+            raise ValueError("tanh_norm: partials must be [S, M, H] with dense rows")
+        pptr, nsplit, stride = _ptr(delta.t), delta.nsplit, delta.split_stride
+    elif delta is not None:
+        _need(delta, dtype, "delta")
+        if delta.shape[-1] != h:
+            raise ValueError("tanh_norm: delta width")
+        dptr = _ptr(delta)
+        dtype = delta.dtype
+    if dtype is None:
+        dtype = torch.float32  # nothing in the storage type is read or written
+    s = _suffix(dtype)
+    if out is not None:
+        _need(out, None, "out")
+        if out.shape[-1] != h:
+            raise ValueError("tanh_norm: widths do not agree")
+    n_rows = out.shape[0] if out is not None else (delta.t.shape[1] if isinstance(delta, Partials) else delta.shape[0] if delta is not None else 0)
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        if rows.numel() < n_rows:
+            raise ValueError("tanh_norm: fewer row indices than output rows")
+    elif resid.shape[0] < n_rows:
+        raise ValueError("tanh_norm: fewer residual rows than output rows")
+    name = f"kvf_tanh_norm_{s}"
+    _check(
+        _fn(name, DECAY_LIB)(_ptr(resid), dptr, pptr, nsplit, stride, mult, _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(out), _ptr(rows), n_rows, h, _stream()),
+        name,
+    )
+
+
+RETENTION_MAX_KEY_DIM = 512  # rows of a head's state that the walk holds in the registers of 32 lanes
+
+
+def retention(
+    x: torch.Tensor, q_off: int, k_off: int, v_off: int, positions: torch.Tensor, inv_freq: torch.Tensor | None, interleaved: bool,
+    k_scale: float, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, qsl: torch.Tensor, state_slots: torch.Tensor,
+    num_seqs: int, num_heads: int, dk: int, dv: int, scratch: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+) -> None:  # fmt: skip
+    """Retention over a flat batch, token by token per sequence, on the float state ``S [heads, dk, dv]`` of each
+    sequence's slot: ``S <- decay[h] S + k v^T``, ``out = S^T q`` (float ``[N, H*dv]``).  Rows of ``x`` hold the
+    projections: ``H`` query heads of ``dk`` from column ``q_off``, key heads from ``k_off``, value heads of ``dv`` from
+    ``v_off``.  The first ``2*len(inv_freq)`` dims of q and k turn with the position (split pairs ``(i, i + rot/2)``
+    unless ``interleaved``), then k is multiplied by ``k_scale``; all of that in float.  ``scratch``: float buffers
+    ``(qn [N, H*dk], kn [N, H*dk], vn [N, H*dv])``; without it they are allocated here.  Two launches."""
+    s = _suffix(x.dtype)
+    _rows2d(x, None, "x")
+    n = x.shape[0]
+    h = int(num_heads)
+    if not 0 < dk <= RETENTION_MAX_KEY_DIM or dv <= 0:
+        raise ValueError(f"retention: key heads of 1 to {RETENTION_MAX_KEY_DIM} numbers")
+    if max(q_off, k_off) + h * dk > x.shape[1] or v_off + h * dv > x.shape[1]:
+        raise ValueError("retention: the columns do not fit the rows")
+    _need(positions, torch.int32, "positions")
+    _need(decay, torch.float32, "decay")
+    if decay.numel() != h:
+        raise ValueError("retention: one decay per head")
+    rot = 0
+    if inv_freq is not None and inv_freq.numel():
+        _need(inv_freq, torch.float32, "inv_freq")
+        rot = 2 * inv_freq.numel()
+        if rot > dk:
+            raise ValueError("retention: more frequencies than dk/2")
+    _rows2d(out, torch.float32, "out")
+    if tuple(out.shape) != (n, h * dv):
+        raise ValueError("retention: out must be float [N, H*dv]")
+    sptr, sstride = _state_view(state, h * dk * dv, "retention state")
+    _need(qsl, torch.int32, "query_start_loc")
+    _need(state_slots, torch.int32, "state_slots")
+    if scratch is None:
+        mk = lambda w: torch.empty((n, w), dtype=torch.float32, device=x.device)  # noqa: E731
+        scratch = (mk(h * dk), mk(h * dk), mk(h * dv))
+    qn, kn, vn = scratch
+    for t, w, what in ((qn, h * dk, "qn"), (kn, h * dk, "kn"), (vn, h * dv, "vn")):
+        _need(t, torch.float32, f"scratch {what}")
+        if tuple(t.shape) != (n, w):
+            raise ValueError(f"retention: scratch {what} must be float [{n}, {w}]")
+    name = f"kvf_retention_{s}"
+    _check(
+        _fn(name, DECAY_LIB)(
+            _ptr(x), x.stride(0), int(q_off), int(k_off), int(v_off), _ptr(positions), _ptr(inv_freq) if rot else None, rot,
+            0 if interleaved else 1, float(k_scale), _ptr(decay), sptr, sstride, _ptr(out), out.stride(0), _ptr(qsl), _ptr(state_slots),
+            int(num_seqs), n, h, int(dk), int(dv), _ptr(qn), _ptr(kn), _ptr(vn), _stream(),
+        ),
+        name,
+        2,
     )  # fmt: skip

@@ -81,8 +81,13 @@ class PagedAttention(Mixer):
     ``qk_norm`` (``{"eps": e}``: every query and key head is RMS-normed over its dims, with the tensors
     ``q_norm.weight`` / ``k_norm.weight`` of ``head_dim`` entries shared by the heads, before any rotation),
     ``distance_bias`` (``{"rows": B, "far": D}``: the tensor ``rel [B, num_heads]`` is added to the scaled
-    scores by ``distance_buckets`` of the distance between query and key) and ``keep_first`` (with a
-    window: the first keys of a sequence that every later query sees, at their true positions).
+    scores by ``distance_buckets`` of the distance between query and key), ``keep_first`` (with a
+    window: the first keys of a sequence that every later query sees, at their true positions),
+    ``softcap`` (``c``: a scaled score ``s`` becomes ``c * tanh(s / c)``), ``sink`` (true: the tensor ``sink [num_heads]``;
+    ``exp(sink_h)`` joins the softmax's denominator of head ``h`` without a key or a value) and ``value_mix``
+    (``"source"``: the values as projected are also kept for the later layers of the step; ``"mix"``: the values become
+    ``(1 - lambda) v + lambda v_source`` with the source layer's values of the same token, before they are cached;
+    both declare the scalar tensor ``vmix``, which only ``"mix"`` uses; source and mixing layers have values of one shape).
 
     Rotation of split pairs with equal key and value sizes and no convolution takes the kernels
     of the Llama decoder; anything else (interleaved pairs, a value size of its own, a convolution,
@@ -120,6 +125,13 @@ class PagedAttention(Mixer):
         self.keep_first = int(params.get("keep_first") or 0)
         if self.keep_first < 0 or (self.keep_first and self.window is None):
             raise ValueError("keep_first is a count of keys and needs a window")
+        self.softcap = float(params.get("softcap") or 0.0)
+        if self.softcap < 0:
+            raise ValueError("softcap must be positive")
+        self.has_sink = bool(params.get("sink", False))
+        self.value_mix = params.get("value_mix")
+        if self.value_mix not in (None, "source", "mix"):
+            raise ValueError("value_mix is 'source', 'mix' or None")
         self.q_dim = self.nh * self.d
         self.o_dim = self.nh * self.dv
         self.qkv_dim = (self.nh + self.nkv) * self.d + self.nkv * self.dv
@@ -144,6 +156,10 @@ class PagedAttention(Mixer):
             out["k_norm.weight"] = WeightDecl((d,), kind="vector", init="ones")
         if params.get("distance_bias"):
             out["rel"] = WeightDecl((int(params["distance_bias"]["rows"]), nh), kind="vector", init="small")
+        if params.get("sink"):
+            out["sink"] = WeightDecl((nh,), kind="vector", init="small")
+        if params.get("value_mix"):
+            out["vmix"] = WeightDecl((), kind="vector", init="unit")
         return out
 
     def cache_need(self) -> CacheNeed:
@@ -171,8 +187,10 @@ class PagedAttention(Mixer):
         self.bias = None
         if self.bias_shape is not None:
             self.bias = ops.DistanceBias(weights["rel"].contiguous(), distance_buckets(*self.bias_shape).to(rt.device))
-        # kept first keys and a bias on the scores are the FP32-pipe kernel's alone
-        plain_scores = self.bias is None and not self.keep_first
+        self.sinks = weights["sink"].contiguous() if self.has_sink else None
+        self.v_lambda = weights["vmix"].reshape(1).contiguous() if self.value_mix == "mix" else None
+        # kept first keys, a bias on the scores, capped scores and sinks are not the tcgen05 kernel's
+        plain_scores = self.bias is None and not self.keep_first and not self.softcap and self.sinks is None
         if plain_scores and self.dv == self.d and ops.tcgen05_attention_supported(rt.dtype, self.nh, self.nkv, self.d, False):
             self._query_tile = ops.tcgen05_query_tile(self.nh, self.nkv)
             rt.query_tile_sizes.add(self._query_tile)
@@ -183,9 +201,7 @@ class PagedAttention(Mixer):
         # no table: q and k are stored and used as the projections leave them
         self.inv_freq = table if table is not None else torch.empty(0, dtype=torch.float32, device=rt.device)
         self.interleaved = bool(getattr(self.position, "pairs_interleaved", False))
-        self.general = bool(self.taps) or self.dv != self.d or self.interleaved or self.qk_eps is not None or not plain_scores
-        if self.qk_eps is not None and table is not None and not self.interleaved:
-            raise ValueError("normed heads with a rotation of split pairs are not built (interleaved pairs are)")
+        self.general = bool(self.taps) or self.dv != self.d or self.interleaved or self.qk_eps is not None or not plain_scores or self.value_mix is not None
 
     def _scratch(self, ctx):
         rt = self.rt
@@ -197,6 +213,8 @@ class PagedAttention(Mixer):
         # a bias or kept first keys: the tensor-core kernel takes them with heads of 64 or 128 (and the ranges of any
         # other decode step); elsewhere the FP32 pipes, with short ranges
         special = self.bias is not None or self.keep_first > 0
+        if self.softcap or self.sinks is not None:
+            return decode_scratch(rt, ctx, self.nh, self.nkv, self.d, self.dv, self._tickets, FP32_PIPE_RANGE)
         on_pipes = special and not (self.dv == self.d and ops.mma_attention_supported(rt.dtype, self.nh, self.nkv, self.d, True))
         return decode_scratch(rt, ctx, self.nh, self.nkv, self.d, self.dv, self._tickets, FP32_PIPE_RANGE if on_pipes else None)
 
@@ -250,10 +268,13 @@ class PagedAttention(Mixer):
             mixed = rt.buf("attn.qkv_conv", n, self.qkv_dim)
             ops.causal_conv(qkv, self.w_conv, cache.state, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, mixed, max_query_len=ctx.max_query_len)
             qkv = mixed
-        if self.qk_eps is not None:
+        if self.qk_eps is not None or self.value_mix is not None:
+            # the values of the step's source layer stay in a buffer of their own until the step is over
+            carried = rt.buf("attn.v_source", n, self.nkv * self.dv) if self.value_mix else None
             ops.head_norm_cache(
-                qkv, ctx.positions, self.q_norm_w, self.k_norm_w, self.qk_eps, self.inv_freq, ctx.slot_mappings[cache.group], cache.k, cache.v,
-                self.nh, self.nkv, self.d, self.dv, ctx.block_size, rt.err,
+                qkv, ctx.positions, self.q_norm_w, self.k_norm_w, self.qk_eps or 0.0, self.inv_freq, ctx.slot_mappings[cache.group], cache.k, cache.v,
+                self.nh, self.nkv, self.d, self.dv, ctx.block_size, rt.err, interleaved=self.interleaved,
+                v_keep=carried if self.value_mix == "source" else None, v_first=carried if self.value_mix == "mix" else None, v_lambda=self.v_lambda,
             )  # fmt: skip
         else:
             ops.rope_cache_general(
@@ -266,7 +287,10 @@ class PagedAttention(Mixer):
 
     def attend(self, ctx, q, q_stride, out, cache) -> None:
         scratch, bound, split = None, None, 256
-        common = dict(window=int(self.window or 0), q_stride=q_stride, err=self.rt.err, dv=self.dv, keep_first=self.keep_first, bias=self.bias)
+        common = dict(
+            window=int(self.window or 0), q_stride=q_stride, err=self.rt.err, dv=self.dv, keep_first=self.keep_first, bias=self.bias,
+            softcap=self.softcap, sinks=self.sinks,
+        )  # fmt: skip
         args = (q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens, ctx.num_seqs)
         shape = (self.nh, self.nkv, self.d, self.scale)
         # bfloat16: the decode kernel may lengthen its key ranges from the step's longest context (the merge

@@ -26,8 +26,11 @@ def _stem(prefix: str, name: str) -> str:
 
 @register_block("prenorm")
 class PreNormBlock(Block):
-    """params: ``norm1``, ``mixer``, ``norm2``, ``ffn`` (``PartSpec`` each) and the weight-name
-    stems ``norm1_name``, ``mixer_name``, ``norm2_name``, ``ffn_name`` under the layer's prefix."""
+    """params: ``norm1``, ``mixer``, ``norm2``, ``ffn`` (``PartSpec`` each; ``ffn`` and ``norm2`` may be ``None``: a
+    layer without a feed-forward) and the weight-name stems ``norm1_name``, ``mixer_name``, ``norm2_name``,
+    ``ffn_name`` under the layer's prefix; optional ``residual_mult`` (``m``: ``h = h + m * mixer(norm1(h))`` and the
+    same for the feed-forward; the results are then handed on as ``ops.Scaled``, which the norms must take, and no
+    part adds into the stream by itself)."""
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -39,20 +42,37 @@ class PreNormBlock(Block):
         }
         self.norm1 = build_part("norm", _spec(params["norm1"]), _stem(prefix, names["norm1"]))
         self.mixer = build_part("mixer", _spec(params["mixer"]), _stem(prefix, names["mixer"]))
-        self.norm2 = build_part("norm", _spec(params["norm2"]), _stem(prefix, names["norm2"]))
-        self.ffn = build_part("ffn", _spec(params["ffn"]), _stem(prefix, names["ffn"]))
+        self.norm2 = self.ffn = None
+        if params.get("ffn") is not None:
+            self.norm2 = build_part("norm", _spec(params["norm2"]), _stem(prefix, names["norm2"]))
+            self.ffn = build_part("ffn", _spec(params["ffn"]), _stem(prefix, names["ffn"]))
+        mult = params.get("residual_mult")
+        self.mult = None if mult is None or float(mult) == 1.0 else float(mult)
 
     def sub_parts(self):
-        return [self.norm1, self.mixer, self.norm2, self.ffn]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
 
     def mixer_part(self):
         return self.mixer
 
     def forward(self, ctx, resid, delta, cache):
-        x = self.norm1.forward(ctx, resid, delta)
-        a = self.mixer.forward(ctx, x, cache)
-        x = self.norm2.forward(ctx, resid, a)
-        return self.ffn.forward(ctx, x)
+        if self.mult is None:
+            x = self.norm1.forward(ctx, resid, delta)
+            a = self.mixer.forward(ctx, x, cache)
+            if self.ffn is None:
+                return a
+            x = self.norm2.forward(ctx, resid, a)
+            return self.ffn.forward(ctx, x)
+        keep, ctx.residual = ctx.residual, None  # a result is scaled before it joins the stream
+        try:
+            x = self.norm1.forward(ctx, resid, delta)
+            a = ops.Scaled(self.mixer.forward(ctx, x, cache), self.mult)
+            if self.ffn is None:
+                return a
+            x = self.norm2.forward(ctx, resid, a)
+            return ops.Scaled(self.ffn.forward(ctx, x), self.mult)
+        finally:
+            ctx.residual = keep
 
 
 @register_block("parallel")

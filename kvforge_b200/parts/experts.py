@@ -6,6 +6,10 @@ choice is made on ``s + correction`` (a tensor that shifts the choice, not the w
 the best groups only when the experts form groups; the chosen experts' results are summed with weights
 ``s / (sum of the chosen s + 1e-20)`` (or with the chosen ``s`` as they are).  A shared expert, a feed-forward
 of its own that every token passes, may be added to the sum.
+
+A router may add a bias to its logits (``z = W_router x + b``), and its weights may be a softmax over the chosen
+logits alone (the logits then rank the experts).  A gated expert is ``W_down[e] join(W_gate[e] x, W_up[e] x)`` with
+``join(g, u) = g' sigmoid(alpha g') (u' + shift)``, ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``.
 """
 
 from __future__ import annotations
@@ -27,7 +31,10 @@ class RoutedExperts(FeedForward):
     ``correction [experts]`` is added to the scores for the choice), ``activation`` (``"gelu"``, the exact one, or
     ``"relu2"``, the square of relu), ``score`` (``"sigmoid"`` or ``"softmax"``), ``normalize`` (default true; false:
     the weights are the chosen scores, not divided by their sum) and ``shared`` (the ``PartSpec`` of a feed-forward
-    that runs for every token and is added; its tensors lie under ``shared.``).
+    that runs for every token and is added; its tensors lie under ``shared.``); ``score: "chosen_softmax"`` (the
+    logits rank the experts, the weights are a softmax over the chosen logits alone); ``router_bias`` (true: the
+    tensor ``router.b [E]`` is added to the logits); ``activation: "gated"`` with ``gated: {"limit": l, "alpha": a,
+    "shift": s}`` (each optional; the defaults make SwiGLU): an expert then also has ``e<i>.gate [ff, W]``.
 
     Tensors: ``router [E, W]``, ``correction [E]``, ``e<i>.up [ff, W]``, ``e<i>.down [W, ff]``."""
 
@@ -42,8 +49,15 @@ class RoutedExperts(FeedForward):
         if self.activation not in ops.EXPERT_ACTIVATIONS:
             raise ValueError(f"the experts' activation is one of {sorted(ops.EXPERT_ACTIVATIONS)}")
         self.score = p.get("score", "sigmoid")
-        if self.score not in ("sigmoid", "softmax"):
-            raise ValueError("score must be 'sigmoid' or 'softmax'")
+        if self.score not in ("sigmoid", "softmax", "chosen_softmax"):
+            raise ValueError("score must be 'sigmoid', 'softmax' or 'chosen_softmax'")
+        self.router_bias = bool(p.get("router_bias", False))
+        self.gated = None
+        if self.activation == "gated":
+            g = p.get("gated") or {}
+            self.gated = ops.GatedActivation(float(g.get("limit", float("inf"))), float(g.get("alpha", 1.0)), float(g.get("shift", 0.0)))
+        # the inner size the kernels see: gate and up rows alternate in blocks of 8, so a gated expert is padded with rows of zeros
+        self.ff_pad = -(-self.ff // ops.GATE_UP_BLOCK) * ops.GATE_UP_BLOCK if self.gated else self.ff
         self.normalize = bool(p.get("normalize", True))
         shared = p.get("shared")
         if isinstance(shared, dict):
@@ -60,7 +74,11 @@ class RoutedExperts(FeedForward):
         out = {"router": WeightDecl((e, w), kind="vector", init="normal")}
         if params.get("correction", True):
             out["correction"] = WeightDecl((e,), kind="vector", init="zeros")
+        if params.get("router_bias"):
+            out["router.b"] = WeightDecl((e,), kind="vector", init="zeros")
         for i in range(e):
+            if params.get("activation") == "gated":
+                out[f"e{i}.gate"] = WeightDecl((ff, w))
             out[f"e{i}.up"] = WeightDecl((ff, w))
             out[f"e{i}.down"] = WeightDecl((w, ff))
         return out
@@ -82,8 +100,20 @@ class RoutedExperts(FeedForward):
         super().bind(weights, rt)
         self.router = weights["router"].contiguous()
         self.correction = weights["correction"].contiguous() if self.corrected else None
-        self.w_up = torch.stack([weights[f"e{i}.up"] for i in range(self.experts)]).contiguous()
-        self.w_down = torch.stack([weights[f"e{i}.down"] for i in range(self.experts)]).contiguous()
+        self.bias = weights["router.b"].contiguous() if self.router_bias else None
+        if self.gated is None:
+            self.w_up = torch.stack([weights[f"e{i}.up"] for i in range(self.experts)]).contiguous()
+            self.w_down = torch.stack([weights[f"e{i}.down"] for i in range(self.experts)]).contiguous()
+        else:
+            # rows of zeros up to a multiple of 8 (a gate of zero gives zero whatever its up row holds), then gate and
+            # up rows in alternating blocks of 8: the products' threads find a gate and its up side by side
+            pad = self.ff_pad - self.ff
+
+            def rows(t):
+                return torch.cat([t, t.new_zeros((pad, t.shape[1]))]) if pad else t
+
+            self.w_up = torch.stack([ops.interleave_gate_up(rows(weights[f"e{i}.gate"]), rows(weights[f"e{i}.up"])) for i in range(self.experts)]).contiguous()
+            self.w_down = torch.stack([torch.cat([weights[f"e{i}.down"], weights[f"e{i}.down"].new_zeros((self.hidden, pad))], dim=1) if pad else weights[f"e{i}.down"] for i in range(self.experts)]).contiguous()
         self._meta = torch.zeros(4, dtype=torch.int32, device=rt.device)
 
     def forward(self, ctx, x: torch.Tensor):
@@ -92,34 +122,37 @@ class RoutedExperts(FeedForward):
         pairs_cap = rt.max_tokens * top
         ids = rt.buf("experts.ids", n, top, torch.int32)
         wts = rt.buf("experts.weights", n, top, torch.float32)
-        ops.moe_route(x, self.router, self.correction, top, self.groups, self.keep, WEIGHT_SUM_EPS, ids, wts, self.score == "softmax", self.normalize)
+        ops.moe_route(
+            x, self.router, self.correction, top, self.groups, self.keep, WEIGHT_SUM_EPS, ids, wts, self.score == "softmax", self.normalize,
+            bias=self.bias, chosen_softmax=self.score == "chosen_softmax",
+        )  # fmt: skip
         scratch = {
             "order": rt.buf("experts.order", n * top, 1, torch.int32, cap=pairs_cap),
             "tiles": rt.buf("experts.tiles", ops.moe_max_tiles(n * top, e), 3, torch.int32, cap=ops.moe_max_tiles(pairs_cap, e)),
             "meta": self._meta,
-            "act": rt.buf("experts.act", n * top, self.ff, cap=pairs_cap),
+            "act": rt.buf("experts.act", n * top, self.ff_pad, cap=pairs_cap),
             "y": rt.buf("experts.y", n * top, self.hidden, torch.float32, cap=pairs_cap),
         }
         if x.dtype == torch.bfloat16 and n * top >= ops.GROUPED_TCGEN05_MIN_ROWS * e:
             scratch["xs"] = rt.buf("experts.xs", n * top, self.hidden, cap=pairs_cap)
         resid = getattr(ctx, "residual", None)
         if resid is not None and resid.shape[0] >= n and resid.shape[1] == self.hidden:
-            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, resid[:n], rt.err, self.activation)
+            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, resid[:n], rt.err, self.activation, self.gated)
             return self.shared.forward(ctx, x) if self.shared is not None else ops.ADDED
         if self.shared is not None:
             # the shared expert first: when its result comes as the float slices of a split product, the routed sum is
             # added into the first slice and the slices are handed on as they are (whoever reads them adds them in order)
             y = self.shared.forward(ctx, x)
             if isinstance(y, ops.Partials) and y.t.dtype == torch.float32 and y.t.shape[1] >= n and y.t.shape[2] == self.hidden:
-                ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, y.t[0, :n], rt.err, self.activation)
+                ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, y.t[0, :n], rt.err, self.activation, self.gated)
                 return y
             out = rt.buf("experts.out", n, self.hidden, torch.float32)
             out.zero_()
-            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out, rt.err, self.activation)
+            ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out, rt.err, self.activation, self.gated)
             if y is not None and y is not ops.ADDED:
                 ops.add_residual(out, y[:n])
             return ops.Partials(out.view(1, n, self.hidden))
         out = rt.buf("experts.out", n, self.hidden, torch.float32)
         out.zero_()
-        ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out, rt.err, self.activation)
+        ops.moe_experts(x, self.w_up, self.w_down, ids, wts, scratch, out, rt.err, self.activation, self.gated)
         return ops.Partials(out.view(1, n, self.hidden))

@@ -29,13 +29,16 @@ TENSOR_CORE_RANGE = 128
 class LatentAttention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``head_dim`` (a query's and key's part that does not turn),
     ``rot_dim`` (the part that does), ``v_head_dim``, ``kv_rank``, ``eps`` (of the latent's norm), ``scale``;
-    optional ``window`` (keys a query sees, itself included), ``position`` (a rotary ``PartSpec`` with
-    interleaved pairs over at most ``rot_dim`` dims, or ``None``) and ``gate`` (``"sigmoid"``: every head's
-    result is multiplied by the logistic function of one more projection of the input, or ``None``).
+    optional ``window`` (keys a query sees, itself included), ``position`` (a rotary ``PartSpec`` over at most
+    ``rot_dim`` dims, interleaved or split pairs, or ``None``), ``gate`` (``"sigmoid"``: every head's result is
+    multiplied by the logistic function of one more projection of the input, one number a head; ``"sigmoid_channel"``:
+    one number for every channel of every head; or ``None``) and ``q_rank`` (the queries come through a latent of
+    their own: ``c_q = rmsnorm(W_dq x)`` with the weight ``dq.norm`` and ``eps``, ``q = W_uq c_q``).
 
-    Tensors: ``q [H*(head_dim+rot_dim), W]`` (one head after the other, in each the part that does not turn first),
+    Tensors: ``q [H*(head_dim+rot_dim), W]`` (one head after the other, in each the part that does not turn first), or
+    with ``q_rank`` ``dq [q_rank, W]``, ``dq.norm [q_rank]`` and ``uq [H*(head_dim+rot_dim), q_rank]``;
     ``dkv [kv_rank+rot_dim, W]``, ``dkv.norm [kv_rank]``, ``uk [H*head_dim, kv_rank]``,
-    ``uv [H*v_head_dim, kv_rank]``, ``g [H, W]`` (with a gate), ``o [W, H*v_head_dim]``."""
+    ``uv [H*v_head_dim, kv_rank]``, ``g [H, W]`` or ``[H*v_head_dim, W]`` (with a gate), ``o [W, H*v_head_dim]``."""
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -47,8 +50,10 @@ class LatentAttention(Mixer):
         if self.window is not None and int(self.window) <= 0:
             raise ValueError("window must be positive")
         self.gated = p.get("gate") is not None
-        if self.gated and p["gate"] != "sigmoid":
-            raise ValueError("the gate of latent attention is 'sigmoid' or None")
+        if self.gated and p["gate"] not in ("sigmoid", "sigmoid_channel"):
+            raise ValueError("the gate of latent attention is 'sigmoid', 'sigmoid_channel' or None")
+        self.gate_cols = 0 if not self.gated else self.nh * (self.dv if p["gate"] == "sigmoid_channel" else 1)
+        self.q_rank = int(p.get("q_rank") or 0)
         if self.dr % 2 or self.rank % 8 or (self.rank + self.dr) % 8 or self.dk % 8 or self.dv % 8:
             raise ValueError("latent attention needs an even rot_dim and sizes that are multiples of 8")
         ops.check_head_dim(self.rank + self.dr, ops.MAX_KEY_DIM)
@@ -59,17 +64,22 @@ class LatentAttention(Mixer):
         self.position_spec: PartSpec | None = pos
         self.position = None
         self.q_cols = self.nh * (self.dk + self.dr)
-        self.c_off = self.q_cols
-        self.g_off = self.q_cols + self.rank + self.dr
-        self.in_dim = -(-(self.g_off + (self.nh if self.gated else 0)) // 8) * 8
+        # the first product's rows: the queries (or their latent), the keys' and values' latent with the shared key part, the gate
+        self.c_off = self.q_rank or self.q_cols
+        self.g_off = self.c_off + self.rank + self.dr
+        self.in_dim = -(-(self.g_off + self.gate_cols) // 8) * 8
         self.d = self.rank + self.dr
 
     @classmethod
     def weight_decls(cls, params):
         w, h = int(params["hidden_size"]), int(params["num_heads"])
         dk, dr, dv, r = (int(params[k]) for k in ("head_dim", "rot_dim", "v_head_dim", "kv_rank"))
+        qr = int(params.get("q_rank") or 0)
+        queries = {"q": WeightDecl((h * (dk + dr), w))}
+        if qr:
+            queries = {"dq": WeightDecl((qr, w)), "dq.norm": WeightDecl((qr,), kind="vector", init="ones"), "uq": WeightDecl((h * (dk + dr), qr), init="wide")}
         out = {
-            "q": WeightDecl((h * (dk + dr), w)),
+            **queries,
             "dkv": WeightDecl((r + dr, w)),
             "dkv.norm": WeightDecl((r,), kind="vector", init="ones"),
             "uk": WeightDecl((h * dk, r), init="wide"),
@@ -77,7 +87,7 @@ class LatentAttention(Mixer):
             "o": WeightDecl((w, h * dv)),
         }
         if params.get("gate") is not None:
-            out["g"] = WeightDecl((h, w))
+            out["g"] = WeightDecl((h * dv if params["gate"] == "sigmoid_channel" else h, w))
         return out
 
     def cache_need(self) -> CacheNeed:
@@ -87,7 +97,9 @@ class LatentAttention(Mixer):
 
     def bind(self, weights, rt):
         super().bind(weights, rt)
-        parts = [weights["q"], weights["dkv"]] + ([weights["g"]] if self.gated else [])
+        parts = [weights["dq"] if self.q_rank else weights["q"], weights["dkv"]] + ([weights["g"]] if self.gated else [])
+        self.w_uq = weights["uq"].contiguous() if self.q_rank else None
+        self.cq_weight = weights["dq.norm"] if self.q_rank else None
         rows = sum(t.shape[0] for t in parts)
         if rows < self.in_dim:  # rows of zeros up to a multiple of 8: the products want aligned widths
             parts.append(torch.zeros((self.in_dim - rows, self.hidden), dtype=parts[0].dtype, device=parts[0].device))
@@ -106,8 +118,7 @@ class LatentAttention(Mixer):
             self.position = build_part("position", self.position_spec)
             self.position.bind({}, rt)
         table = self.position.table() if self.position is not None else None
-        if table is not None and not getattr(self.position, "pairs_interleaved", False):
-            raise ValueError("latent attention turns interleaved pairs")
+        self.interleaved = bool(getattr(self.position, "pairs_interleaved", False))
         self.inv_freq = table
 
     def _per_head(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -132,12 +143,23 @@ class LatentAttention(Mixer):
         else:
             ops.linear(x, self.w_in, y)
         qa = rt.buf("latent.qa", n, h * d)
+        q = None
+        if self.q_rank:
+            # the queries' latent, normed, and the queries made from it
+            cq = rt.buf("latent.cq", n, self.q_rank)
+            ops.row_rmsnorm(y[:, : self.q_rank], self.cq_weight, self.eps, cq)
+            q = rt.buf("latent.q", n, self.q_cols)
+            if ops.skinny_ok(cq, self.w_uq):
+                ops.gemm_skinny(cq, self.w_uq, q)
+            else:
+                ops.linear(cq, self.w_uq, q)
         ops.latent_prepare(
             y, 0, self.c_off, ctx.positions, self.c_weight, self.eps, self.inv_freq, ctx.slot_mappings[cache.group], cache.k, qa,
-            h, dk, dr, r, ctx.block_size, rt.err,
+            h, dk, dr, r, ctx.block_size, rt.err, interleaved=self.interleaved, q=q,
         )  # fmt: skip
         # the key up-projection folded into the queries
-        self._per_head(y[:, : self.q_cols].view(n, h, dk + dr)[:, :, :dk], self.w_uk, qa.view(n, h, d)[:, :, :r])
+        q_heads = (q if q is not None else y[:, : self.q_cols]).view(n, h, dk + dr)
+        self._per_head(q_heads[:, :, :dk], self.w_uk, qa.view(n, h, d)[:, :, :r])
         o_lat = rt.buf("latent.o", n, h * r)
         tensor_cores = ops.latent_attention_supported(qa.dtype, d, r)
         scratch, bound, split = None, None, 256
@@ -159,5 +181,7 @@ class LatentAttention(Mixer):
         out = rt.buf("latent.out", n, h * dv)
         self._per_head(o_lat.view(n, h, r), self.w_uv, out.view(n, h, dv))
         if self.gated:
-            ops.head_gate(out, y[:, self.g_off : self.g_off + h], h, dv)
+            # one number a head, or one a channel (the same kernel over "heads" of one channel)
+            per = dv if self.gate_cols == h else 1
+            ops.head_gate(out, y[:, self.g_off : self.g_off + self.gate_cols], self.gate_cols, per)
         return project(rt, "attn.proj", out, self.w_o, ctx)

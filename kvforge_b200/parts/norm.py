@@ -104,3 +104,34 @@ class LayerNorm(Norm):
     def replace(self, ctx, resid: torch.Tensor, out: torch.Tensor | None = None) -> None:
         """The stream itself becomes its normed rows (float); ``out`` gets them in the storage type."""
         ops.norm_step(resid, None, self.weight, out, self.eps, self.centred, store_normed=True)
+
+
+@register_norm("tanh_norm")
+class TanhNorm(Norm):
+    """A norm that computes no mean and no variance: ``tanh(alpha * x) * w + b`` per number, with a learned scalar
+    ``alpha``, in 32-bit.  params: ``dim``.  Tensors: ``weight [dim]``, ``alpha []``, ``bias [dim]``.  What the
+    sublayer before left pending may be an ``ops.Scaled``: it joins the stream multiplied by a constant."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.dim = int(params["dim"])
+
+    @classmethod
+    def weight_decls(cls, params):
+        d = int(params["dim"])
+        return {
+            "weight": WeightDecl((d,), kind="vector", init="ones"),
+            "alpha": WeightDecl((), kind="vector", init="half"),
+            "bias": WeightDecl((d,), kind="vector", init="zeros"),
+        }
+
+    def bind(self, weights, rt):
+        super().bind(weights, rt)
+        self.weight, self.bias = weights["weight"], weights["bias"]
+        self.alpha = weights["alpha"].reshape(1).contiguous()
+
+    def forward(self, ctx, resid: torch.Tensor, delta, rows: torch.Tensor | None = None, num_rows: int | None = None):
+        n = num_rows if rows is not None else resid.shape[0]
+        out = self.rt.buf("norm.out" if rows is None else "norm.rows", n, self.dim)
+        ops.tanh_norm(resid, delta, self.alpha, self.weight, self.bias, out, rows)
+        return out

@@ -54,6 +54,10 @@ def draw(name: str, decl: WeightDecl, seed: int, device: torch.device | str = "c
         w = decl.shape[0]
         t = torch.cat([torch.eye(w, dtype=torch.float32, device=device), torch.zeros((w, decl.shape[1] - w), dtype=torch.float32, device=device)], dim=1)
         return t + init_std * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
+    if decl.init == "half":  # a positive scale of order one half (the slope of a norm without statistics)
+        return 0.5 + 0.1 * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
+    if decl.init == "unit":  # a number between 0 and 1 (a mixing proportion)
+        return torch.rand(decl.shape, generator=g, dtype=torch.float32, device=device)
     if decl.init == "wide":  # the second matrix of a low-rank pair: its input is small already
         return (decl.shape[-1] ** -0.5) * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
     return init_std * torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
