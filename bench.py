@@ -601,12 +601,13 @@ def run_load(cfg, nreq: int, short_prompts: bool = False) -> dict:
 
 
 DESIGN_PAIRS = (("mopilorn-1b", "llama-3.2-1b"), ("mopilorn-3b", "llama-3.2-3b"), ("setenex-1b", "llama-3.2-1b"), ("gukirax-1b", "llama-3.2-1b"),
-                ("gukirax-3b", "llama-3.2-3b"))  # fmt: skip
+                ("gukirax-3b", "llama-3.2-3b"), ("sonalix-1b", "setenex-1b"))  # fmt: skip
 
 
 def run_designs(args) -> dict:
     """Prompt and decode throughput of the Mopilorn, Setenex and Gukirax shapes beside the Llama shapes of equal width,
-    depth, feed-forward per token and vocabulary (random weights): a prompt of 2,048 tokens, and decode steps of 8
+    depth, feed-forward per token and vocabulary, and of the Sonalix shape beside the Setenex shape, its nearest
+    relative (random weights): a prompt of 2,048 tokens, and decode steps of 8
     and 64 requests with 2,048 tokens behind them, each as captured graphs, timed on the device.  ``--design NAME``
     runs the one pair that holds the named shape."""
     import gc
@@ -856,7 +857,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "attention", "attention-prefill", "gemm", "sample", "load", "designs"], help="run one part alone and print a short line (for profiling); 'designs': the Mopilorn, Setenex and Gukirax shapes beside the Llama shapes of equal size")
+    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "attention", "attention-prefill", "gemm", "sample", "load", "designs"], help="run one part alone and print a short line (for profiling); 'designs': the Mopilorn, Setenex, Gukirax and Sonalix shapes beside the shapes of equal size they are compared with")
     ap.add_argument("--design", default=None, help="with --only designs: the one pair that holds this named shape (default: all pairs)")
     ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b, mopilorn-1b, mopilorn-3b)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")

@@ -262,7 +262,8 @@ def patterned(
 
 
 # Named shapes with random weights: a small one for demonstrations, and one with the width, depth and vocabulary of the
-# 1B Llama shape this engine is measured on (a token's feed-forward has that shape's flops: 4 of 32 experts of 2,048).
+# 1B Llama shape this engine is measured on (a token's feed-forward has that shape's flops: 4 of 32 experts of three
+# matrices of 1,408 where the Setenex shape of that size has two of 2,048).
 SONALIX_PRESETS: dict[str, SonalixConfig] = {
     "sonalix-tiny": patterned(
         vocab=256, width=96, pattern="arl", repeats=1, heads=4, kv_heads=2, dim=32, window=24, softcap=15.0, ret_heads=2, ret_dim=16,
@@ -270,7 +271,7 @@ SONALIX_PRESETS: dict[str, SonalixConfig] = {
     ),
     "sonalix-1b": patterned(
         vocab=128256, width=2048, pattern="aral", repeats=4, heads=32, kv_heads=8, dim=64, window=1024, softcap=30.0, ret_heads=16,
-        ret_dim=128, latent_heads=16, latent_dim=128, rot_dim=64, kv_rank=512, q_rank=768, dense_ff=8192, experts=32, top=4, ff=2048,
+        ret_dim=128, latent_heads=16, latent_dim=128, rot_dim=64, kv_rank=512, q_rank=768, dense_ff=8192, experts=32, top=4, ff=1408,
         residual_mult=0.5, base=500000.0,
     ),
 }  # fmt: skip
