@@ -15,9 +15,10 @@ __device__ __forceinline__ uint32_t kvf_pack_bf16x2(float lo, float hi) {
 // CTA runs it: lanes over the ranges for the weights, then lanes over the output dims.
 // wgt: ns floats of shared memory of this warp.  The sums of the first ranges are requested
 // before the weights are worked out, so that both reads wait for memory at the same time.
+// sink: a number whose exponential joins the denominator once (natural-log units; -inf: none).
 template <int D>
 __device__ __forceinline__ void merge_ranges_warp(const float* part_acc, const float* part_ml, size_t base, int ns,
-                                                  float* wgt, bf16* o, int lane) {
+                                                  float* wgt, bf16* o, int lane, float sink = -INFINITY) {
   constexpr int PRE = 8;     // ranges read ahead
   constexpr int JN = D / 64; // float2 per lane and range
   float2 pre[PRE][JN];
@@ -35,7 +36,8 @@ __device__ __forceinline__ void merge_ranges_warp(const float* part_acc, const f
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-  float lsum = 0.f;
+  mx = fmaxf(mx, sink);
+  float lsum = (lane == 0 && sink != -INFINITY) ? __expf(sink - mx) : 0.f;
   for (int s = lane; s < ns; s += 32) {
     const float ms = wgt[s];
     const float w = (ms == -INFINITY) ? 0.f : __expf(ms - mx);

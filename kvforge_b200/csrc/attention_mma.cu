@@ -3,7 +3,9 @@
 // this step's writes and q_b queries; query i sits at p = ctx_b - q_b + i and sees key j
 // iff j <= p (and j > p - window when window > 0); softmax in float, one rounding.  The tile
 // Both forms also take, under a window, first keys that stay visible at any distance (j < keep_first)
-// and a bias on the scaled scores by distance and head: bias[head][min(p - j, far)] (float [nh][far + 1]).
+// and a bias on the scaled scores by distance and head: bias[head][min(p - j, far)] (float [nh][far + 1]);
+// a soft cap c on the scaled scores (c * tanh(S / c), before any bias); and a sink a head, a learned number whose
+// exponential joins the softmax's denominator once, without a key or a value.
 //
 // One CTA serves one kv head of one sequence.  The MMA's 16 rows are (query token, head of
 // the group) pairs, so the g query heads that share a kv head share every K/V tile that is
@@ -51,6 +53,9 @@ struct MmaParams {
   int keep_first;
   const float* bias;       // [nh][bias_far + 1]
   int bias_far;
+  // soft cap c on the scaled scores: cap_in = scale / c, cap_out = c * log2(e); cap_out == 0: none
+  float cap_in, cap_out;
+  const float* sinks;      // [nh] (natural-log units) or null
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -175,13 +180,17 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[2
 // lo[r] <= k <= hi[r].  Scores come in as raw dot products and leave as probabilities
 // relative to the new maximum.
 // EXTRA: keys below `keep_first` are seen whatever lo says, and bias[head[r] * (far + 1) + min(qpos[r] - k, far)]
-// is added to the scaled score (qpos[r] is the row's own position).
+// is added to the scaled score (qpos[r] is the row's own position); with cap_out > 0 the scaled score s * scale
+// becomes c * tanh(s * scale / c) first (cap_in = scale / c, cap_out = c * log2(e)).
+// tanh(x) = 1 - 2 / (exp(2x) + 1): exact at both ends, absolute error of a few 1e-7 near zero.
+__device__ __forceinline__ float fast_tanh(float x) { return 1.f - __fdividef(2.f, fast_exp2(x * 2.8853900817779268f) + 1.f); }
+
 template <int NT, int ND, bool EXTRA = false>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4], float (&m)[2], float (&l)[2],
                                              const int (&lo)[2], const int (&hi)[2], int key0, float scale_log2,
                                              int lane, bool need_mask, int keep_first = 0, const float* bias = nullptr,
                                              int far = 0, const int* head = nullptr,
-                                             const int* qpos = nullptr) {
+                                             const int* qpos = nullptr, float cap_in = 0.f, float cap_out = 0.f) {
   float mx[2] = {-INFINITY, -INFINITY};
   // a tile that every row sees whole, with every distance inside the table: no masks, no clamps, and a row's
   // biases for neighbouring keys are neighbouring words below one pointer
@@ -195,6 +204,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float v = s[j][e] * scale_log2;
+        if (cap_out > 0.f) v = cap_out * fast_tanh(s[j][e] * cap_in);
         if (bias) v = fmaf(__ldg(((e >> 1) ? b1 : b0) - (j * 8 + (e & 1))), 1.4426950408889634f, v);
         s[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -211,6 +221,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4
         float v = -INFINITY;
         if (vis) {
           v = s[j][e] * scale_log2;
+          if (cap_out > 0.f) v = cap_out * fast_tanh(s[j][e] * cap_in);
           if (bias) v = fmaf(__ldg(bias + (size_t)head[r] * (far + 1) + min(max(qpos[r] - kp, 0), far)), 1.4426950408889634f, v);
         }
         s[j][e] = v;
@@ -342,7 +353,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
   // tiles that hold kept first keys and lie wholly before the window's first tile are walked first
   const int keep = p.window > 0 ? p.keep_first : 0;
   const int n_keep = min((keep + BN - 1) / BN, kv_lo / BN);
-  const bool extra = keep > 0 || p.bias != nullptr;
+  const bool extra = keep > 0 || p.bias != nullptr || p.cap_out > 0.f;
   // a warp whose rows all lie past the tile's tokens still helps with the loads
   const bool warp_active = (warp * 16) / g < n_tok;
 
@@ -381,7 +392,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
       const int key0 = tile_key0(t);
       const bool need_mask = !rows_full || key0 + BN - 1 > all_hi || key0 < all_lo;
       if (extra)
-        softmax_step<BN / 8, D / 8, true>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_far, head, pos);
+        softmax_step<BN / 8, D / 8, true>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_far, head, pos, p.cap_in, p.cap_out);
       else
         softmax_step<BN / 8, D / 8>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask);
       pv_tile<D, BN / 16>(o, s, vs, 0, lane);
@@ -394,7 +405,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
     if (pos[h] < 0) continue;
     const int r = warp * 16 + (lane >> 2) + 8 * h;
     const int tok = r / g, hh = r - tok * g;
-    const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+    float lsum = l[h], corr = 1.f;
+    if (p.sinks) {  // the sink joins the denominator once, after every key (m is in log2 units)
+      const float sk = p.sinks[kvh * g + hh] * 1.4426950408889634f, mm = fmaxf(m[h], sk);
+      corr = m[h] == -INFINITY ? 0.f : fast_exp2(m[h] - mm);
+      lsum = l[h] * corr + fast_exp2(sk - mm);
+    }
+    const float inv = lsum > 0.f ? corr / lsum : 0.f;
     bf16* dst = p.out + (size_t)(q_begin + q0 + tok) * p.out_stride + (size_t)(kvh * g + hh) * D + ((lane & 3) << 1);
 #pragma unroll
     for (int j = 0; j < D / 8; ++j)
@@ -430,7 +447,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
   const int keep = p.window > 0 ? p.keep_first : 0;
   const int keep_hi = min(min(kv_hi, kv_lo), ((keep + BN - 1) / BN) * BN);
   const int n_keep = keep_hi > key_lo ? (keep_hi - key_lo + BN - 1) / BN : 0;
-  const bool extra = keep > 0 || p.bias != nullptr;
+  const bool extra = keep > 0 || p.bias != nullptr || p.cap_out > 0.f;
   const bool empty = kv_lo >= kv_hi && n_keep == 0;  // wholly before the window, and no kept key
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int* bt = p.block_tables + (size_t)b * p.bt_stride;
@@ -510,7 +527,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
       const int key0 = tile_key0(t) + warp * 16;
       const bool need_mask = key0 < first_seen || key0 + 15 > kv_hi - 1;
       if (extra)
-        softmax_step<2, D / 8, true>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_far, head, qpos);
+        softmax_step<2, D / 8, true>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask, keep, p.bias, p.bias_far, head, qpos, p.cap_in, p.cap_out);
       else
         softmax_step<2, D / 8>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask);
       pv_tile<D, 1>(o, s, vs, warp, lane);
@@ -566,7 +583,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
   bf16* orow = p.out + (size_t)(q_begin + q_len - 1) * p.out_stride;
   for (int h = warp; h < g; h += NWARPS) {
     const int head = kvh * g + h;
-    merge_ranges_warp<D>(p.part_acc, p.part_ml, ((size_t)b * p.nh + head) * p.max_splits, ns, wgt, orow + (size_t)head * D, lane);
+    merge_ranges_warp<D>(p.part_acc, p.part_ml, ((size_t)b * p.nh + head) * p.max_splits, ns, wgt, orow + (size_t)head * D, lane,
+                         p.sinks ? p.sinks[head] : -INFINITY);
   }
 }
 
@@ -576,7 +594,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
 __global__ void __launch_bounds__(128)
 attn_mma_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                       bf16* __restrict__ out, const int* __restrict__ qsl, const int* __restrict__ ctx_lens,
-                      int nh, int d, int out_stride, int split_size, int max_splits) {
+                      int nh, int d, int out_stride, int split_size, int max_splits, const float* __restrict__ sinks) {
   pdl_launch();
   pdl_wait();
   __shared__ float wgt[1024];
@@ -593,8 +611,9 @@ attn_mma_merge_kernel(const float* __restrict__ part_acc, const float* __restric
     wgt[s] = ms;
     mx = fmaxf(mx, ms);
   }
-  const float M = block_max(mx, red);
-  float lsum = 0.f;
+  const float sink = sinks ? sinks[head] : -INFINITY;
+  const float M = fmaxf(block_max(mx, red), sink);
+  float lsum = (threadIdx.x == 0 && sinks) ? __expf(sink - M) : 0.f;
   for (int s = threadIdx.x; s < ns; s += blockDim.x) {
     const float ms = wgt[s];
     const float w = (ms == -INFINITY) ? 0.f : __expf(ms - M);
@@ -630,7 +649,7 @@ int launch_mma(const MmaParams& p, int B, int max_q_len, cudaStream_t st) {
     int rc = launch(kern, dim3(p.grid_splits, B, p.nkv), dim3(NWARPS * 32), need, st, p);
     if (rc || p.tickets) return rc;
     return launch(attn_mma_merge_kernel, dim3(p.nh, B), dim3(128), 0, st, (const float*)p.part_acc,
-                  (const float*)p.part_ml, p.out, p.qsl, p.ctx_lens, p.nh, D, p.out_stride, p.split_size, p.max_splits);
+                  (const float*)p.part_ml, p.out, p.qsl, p.ctx_lens, p.nh, D, p.out_stride, p.split_size, p.max_splits, p.sinks);
   }
   auto kern = attn_mma_tile_kernel<D>;
   if (smem > 48 * 1024) {
@@ -650,9 +669,10 @@ static int run_mma(const void* q, void* out, const void* kcache, const void* vca
                    const int* qsl, const int* ctx_lens, int B, int max_q_len, int q_stride, int out_stride,
                    int bt_stride, int nh, int nkv, int d, int block_size, float scale, int window, int split_size,
                    int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, cudaStream_t st,
-                   int keep_first = 0, const float* bias = nullptr, int bias_far = 0) {
+                   int keep_first = 0, const float* bias = nullptr, int bias_far = 0, float softcap = 0.f,
+                   const float* sinks = nullptr) {
   if (B <= 0 || max_q_len <= 0) return 0;
-  if (keep_first < 0 || (bias && bias_far < 0)) return (int)cudaErrorInvalidValue;
+  if (keep_first < 0 || (bias && bias_far < 0) || softcap < 0.f) return (int)cudaErrorInvalidValue;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || block_size <= 0) return (int)cudaErrorInvalidValue;
   const int g = nh / nkv;
   if (g > BM || (unsigned)B > 65535u || (unsigned)nkv > 65535u) return (int)cudaErrorInvalidValue;
@@ -670,6 +690,9 @@ static int run_mma(const void* q, void* out, const void* kcache, const void* vca
   p.grid_splits = grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.keep_first = keep_first; p.bias = bias; p.bias_far = bias_far;
+  p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_out = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.sinks = sinks;
   if (split_size > 0) {
     if (g > 16 || split_size % BN != 0 || max_splits <= 0 || max_splits > 1024 || !part_acc || !part_ml || max_q_len != 1)
       return (int)cudaErrorInvalidValue;
@@ -687,24 +710,27 @@ KVF_API int kvf_paged_attention_mma_bf16(const void* q, void* out, const void* k
                  nkv, d, block_size, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, nullptr, st);
 }
 
-// The tile form with first keys that stay visible under the window and a bias by distance (see the top of this file).
+// The tile form with first keys that stay visible under the window, a bias by distance, capped scores and sinks (see
+// the top of this file).
 KVF_API int kvf_paged_attention_mma_biased_bf16(const void* q, void* out, const void* kcache, const void* vcache,
                                                 const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                                 int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
                                                 int nkv, int d, int block_size, float scale, int window, int keep_first,
-                                                const float* bias, int bias_far, cudaStream_t st) {
+                                                const float* bias, int bias_far, float softcap, const float* sinks,
+                                                cudaStream_t st) {
   return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len, q_stride, out_stride, bt_stride, nh,
-                 nkv, d, block_size, scale, window, 0, 0, 0, nullptr, nullptr, nullptr, st, keep_first, bias, bias_far);
+                 nkv, d, block_size, scale, window, 0, 0, 0, nullptr, nullptr, nullptr, st, keep_first, bias, bias_far, softcap,
+                 sinks);
 }
 
-// The split form in one launch (see below) with kept first keys and a bias by distance.
+// The split form in one launch (see below) with kept first keys, a bias by distance, capped scores and sinks.
 KVF_API int kvf_paged_attention_decode_biased_bf16(const void* q, void* out, const void* kcache, const void* vcache,
                                                    const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                                    int q_stride, int out_stride, int bt_stride, int nh, int nkv, int d,
                                                    int block_size, float scale, int window, int split_size,
                                                    int max_splits, int grid_splits, float* part_acc, float* part_ml,
                                                    int* tickets, int keep_first, const float* bias, int bias_far,
-                                                   cudaStream_t st);
+                                                   float softcap, const float* sinks, cudaStream_t st);
 
 // The split form in one launch: `tickets` holds B * nkv counters that are zero before the first
 // launch (each launch leaves them zero); the CTA that finishes last among the ranges of a
@@ -726,9 +752,9 @@ KVF_API int kvf_paged_attention_decode_biased_bf16(const void* q, void* out, con
                                                    int block_size, float scale, int window, int split_size,
                                                    int max_splits, int grid_splits, float* part_acc, float* part_ml,
                                                    int* tickets, int keep_first, const float* bias, int bias_far,
-                                                   cudaStream_t st) {
+                                                   float softcap, const float* sinks, cudaStream_t st) {
   if (!tickets || split_size <= 0) return (int)cudaErrorInvalidValue;
   return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, 1, q_stride, out_stride, bt_stride, nh, nkv, d,
                  block_size, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, tickets, st, keep_first, bias,
-                 bias_far);
+                 bias_far, softcap, sinks);
 }

@@ -9,10 +9,11 @@
 //   prepare : a warp per (token, head of q, k or v): rotation, scaling, widening to float.  Nothing here depends
 //             on the state, so it runs over all tokens at once.
 //   walk    : a CTA owns (sequence, head, tile of CT value columns) and walks the sequence's tokens in order.  A
-//             column's dk rows are spread over KS neighbouring lanes, R rows each in registers (row i*KS + s for lane
-//             s).  Per token a lane makes  S <- a S + k v  and its part of  S^T q  in one pass; the KS parts are
-//             added in a fixed tree.  Chunks of TC tokens come in through a cp.async double buffer; the state
-//             tile passes through shared memory so that global memory sees whole rows.
+//             column's dk rows are spread over KS neighbouring lanes, R rows each in registers (in runs of four: rows
+//             4 (j KS + s) .. + 3 for lane s, so that q and k come from shared memory four at a time).  Per token a
+//             lane makes  S <- a S + k v  and its part of  S^T q  in one pass; the KS parts are added in a fixed
+//             tree.  Chunks of TC tokens come in through a cp.async double buffer; the state tile passes through
+//             shared memory so that global memory sees whole rows.
 //
 // The state after a token is the same bits however the sequence was cut into steps (the walk is token by token,
 // and every sum has an order fixed by dk alone), so a token's output does not depend on the cut, the batch or
@@ -108,9 +109,10 @@ __global__ void __launch_bounds__(128) retention_walk_kernel(const float* __rest
   // what no copy ever writes is zero for good: rows of q and k beyond dk, value columns beyond the tile's
   for (int idx = tid; idx < 2 * stage; idx += nthreads) buf[idx] = 0.f;
   __syncthreads();
+  // register i of lane s holds row ((i / 4) * KS + s) * 4 + i % 4
   float S[R];
 #pragma unroll
-  for (int i = 0; i < R; ++i) S[i] = St[(i * KS + s) * lds + col];
+  for (int i = 0; i < R; ++i) S[i] = St[(((i >> 2) * KS + s) * 4 + (i & 3)) * lds + col];
 
   const bool wide_qk = (dk & 3) == 0, wide_v = (dv & 3) == 0 && (c0 & 3) == 0 && (ncol & 3) == 0;
   auto issue = [&](int chunk) {
@@ -145,14 +147,21 @@ __global__ void __launch_bounds__(128) retention_walk_kernel(const float* __rest
     const float* bv = bk + TC * dkp;
     const int t0 = c * TC, nt = min(TC, q_len - t0);
     for (int t = 0; t < nt; ++t) {
-      const float* q = bq + t * dkp + s;
-      const float* k = bk + t * dkp + s;
+      const float4* q = reinterpret_cast<const float4*>(bq + t * dkp) + s;
+      const float4* k = reinterpret_cast<const float4*>(bk + t * dkp) + s;
       const float vv = bv[t * CT + col];
       float p = 0.f;
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        S[i] = fmaf(a, S[i], __fmul_rn(k[i * KS], vv));
-        p = fmaf(S[i], q[i * KS], p);
+      for (int j = 0; j < R / 4; ++j) {
+        const float4 k4 = k[j * KS], q4 = q[j * KS];
+        S[4 * j] = fmaf(a, S[4 * j], __fmul_rn(k4.x, vv));
+        p = fmaf(S[4 * j], q4.x, p);
+        S[4 * j + 1] = fmaf(a, S[4 * j + 1], __fmul_rn(k4.y, vv));
+        p = fmaf(S[4 * j + 1], q4.y, p);
+        S[4 * j + 2] = fmaf(a, S[4 * j + 2], __fmul_rn(k4.z, vv));
+        p = fmaf(S[4 * j + 2], q4.z, p);
+        S[4 * j + 3] = fmaf(a, S[4 * j + 3], __fmul_rn(k4.w, vv));
+        p = fmaf(S[4 * j + 3], q4.w, p);
       }
       for (int o = KS >> 1; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
       if (s == 0 && col < ncol) out[(size_t)(q_begin + t0 + t) * out_stride + (size_t)h * dv + c0 + col] = p;
@@ -161,7 +170,7 @@ __global__ void __launch_bounds__(128) retention_walk_kernel(const float* __rest
   }
   asm volatile("cp.async.wait_group 0;\n" ::);
 #pragma unroll
-  for (int i = 0; i < R; ++i) St[(i * KS + s) * lds + col] = S[i];
+  for (int i = 0; i < R; ++i) St[(((i >> 2) * KS + s) * 4 + (i & 3)) * lds + col] = S[i];
   __syncthreads();
   for (int idx = tid; idx < dk * ncol; idx += nthreads) {
     const int r = idx / ncol, c = idx - r * ncol;

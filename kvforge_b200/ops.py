@@ -26,9 +26,9 @@ _SIGNATURES = {
     "kvf_cast_from_float_{s}": "pplp",
     "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiiifiiiippiipifpp",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
-    "kvf_paged_attention_mma_biased_bf16": "pppppppiiiiiiiiifiipip",
+    "kvf_paged_attention_mma_biased_bf16": "pppppppiiiiiiiiifiipifpp",
     "kvf_latent_attention_bf16": "ppppppiiiiiiiiifiiiippp",
-    "kvf_paged_attention_decode_biased_bf16": "pppppppiiiiiiiifiiiipppipip",
+    "kvf_paged_attention_decode_biased_bf16": "pppppppiiiiiiiifiiiipppipifpp",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
     "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppiip",
@@ -582,13 +582,13 @@ def paged_attention(
     context, over all pairs, are at most this many (``attention_wave_target``).
     """
     s = _suffix(q.dtype)
-    capped = float(softcap) > 0.0 or sinks is not None  # the FP32-pipe kernel's alone
+    capped = float(softcap) > 0.0 or sinks is not None
     if float(softcap) < 0.0:
         raise ValueError("paged_attention: softcap must be positive (0: none)")
     special = vcache is kcache or keep_first > 0 or bias is not None or d > 256 or (dv or d) > 256 or capped
     # kept first keys and a bias alone, on heads of 64 or 128 in bfloat16 with many queries: the tile form of the mma.sync kernel
     biased_mma = (
-        special and not capped and vcache is not kcache and (dv or d) == d and kernel == "auto"
+        special and vcache is not kcache and (dv or d) == d and kernel == "auto"
         and mma_attention_supported(q.dtype, nh, nkv, d, scratch is not None) and (q_stride or q.shape[-1]) % 2 == 0 and out.shape[-1] % 2 == 0
         and (scratch is None or len(scratch) > 2)
     )  # fmt: skip
@@ -671,7 +671,7 @@ def paged_attention(
             _fn(name)(
                 _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
                 num_seqs, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
-                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), int(keep_first), *bias_args, _stream(),
+                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), int(keep_first), *bias_args, float(softcap), _ptr(sinks), _stream(),
             ),
             name,
         )  # fmt: skip
@@ -682,7 +682,7 @@ def paged_attention(
             _fn(name)(
                 _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
                 num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale), int(window),
-                int(keep_first), *bias_args, _stream(),
+                int(keep_first), *bias_args, float(softcap), _ptr(sinks), _stream(),
             ),
             name,
         )  # fmt: skip

@@ -212,9 +212,7 @@ class PagedAttention(Mixer):
             self._tickets = torch.zeros(seqs * self.nkv, dtype=torch.int32, device=rt.device)
         # a bias or kept first keys: the tensor-core kernel takes them with heads of 64 or 128 (and the ranges of any
         # other decode step); elsewhere the FP32 pipes, with short ranges
-        special = self.bias is not None or self.keep_first > 0
-        if self.softcap or self.sinks is not None:
-            return decode_scratch(rt, ctx, self.nh, self.nkv, self.d, self.dv, self._tickets, FP32_PIPE_RANGE)
+        special = self.bias is not None or self.keep_first > 0 or bool(self.softcap) or self.sinks is not None
         on_pipes = special and not (self.dv == self.d and ops.mma_attention_supported(rt.dtype, self.nh, self.nkv, self.d, True))
         return decode_scratch(rt, ctx, self.nh, self.nkv, self.d, self.dv, self._tickets, FP32_PIPE_RANGE if on_pipes else None)
 

@@ -331,11 +331,12 @@ def attention_part(width, m, eps, role):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window,cap", [(None, None), (7, 4.0), (33, 50.0), (1, 9.0), (70, None)])
-@pytest.mark.parametrize("dk,dv,rot,t", [(24, 16, 8, 45), (64, 64, 64, 200), (128, 48, 2, 150)])
+@pytest.mark.parametrize("dk,dv,rot,t", [(24, 16, 8, 45), (64, 64, 64, 200), (128, 48, 2, 150), (128, 128, 64, 150)])
 def test_attention_with_caps_sinks_and_mixed_values(dtype, window, cap, dk, dv, rot, t):
     """Two layers in one step: the first keeps its values for the second, which mixes them into its own before it caches
     them.  The whole sequence in one step, then portions and single tokens on top of the cache (the decode form: key
-    ranges in parallel, the sink counted once), against the plain mixer."""
+    ranges in parallel, the sink counted once), against the plain mixer.  Heads of 64 and of 128 with values as wide go
+    to the tensor-core kernels in bfloat16 (tiles of 64 keys for prompts and portions, key ranges for single tokens)."""
     from kvforge_b200.parts.base import LayerCache
 
     rt = runtime(dtype)
