@@ -11,13 +11,13 @@
 //   walk    : a CTA owns (sequence, head, tile of CT value columns) and walks the sequence's tokens in order.  A
 //             column's dk rows are spread over KS neighbouring lanes, R rows each in registers (in runs of four: rows
 //             4 (j KS + s) .. + 3 for lane s, so that q and k come from shared memory four at a time).  Per token a
-//             lane makes  S <- a S + k v  and its part of  S^T q  in one pass; the KS parts are added in a fixed
-//             tree.  Chunks of TC tokens come in through a cp.async double buffer; the state tile passes through
+//             lane makes  S <- a S + k v  and its part of  S^T q  in one pass; the parts are added in a tree whose
+//             shape follows dk alone.  Chunks of TC tokens come in through a cp.async double buffer; the state tile passes through
 //             shared memory so that global memory sees whole rows.
 //
 // The state after a token is the same bits however the sequence was cut into steps (the walk is token by token,
-// and every sum has an order fixed by dk alone), so a token's output does not depend on the cut, the batch or
-// the slot.  A sequence without rows, or with a slot below zero (padding), touches nothing.
+// and every sum has an order fixed by dk alone, however many rows a lane holds), so a token's output does not
+// depend on the cut, the batch or the slot.  A sequence without rows, or with a slot below zero (padding), touches nothing.
 #include "common.cuh"
 
 using namespace kvf;
@@ -76,9 +76,13 @@ __device__ __forceinline__ void cp_async(float* dst, const float* src, bool wide
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src));
 }
 
-// R rows a lane; blockDim.x = KS * CT (a multiple of 32, at most 128); KS a power of two, at most 32.
+// R rows a lane (a multiple of four); blockDim.x = KS * CT (a multiple of 32, at most 256); KS a power of two, at most 32.
+// The sum over a column's rows has one order whatever R is: runs of four rows are added in order, and the runs are then
+// added in a binary tree that joins the halves of the (padded) row range first and neighbouring runs last; a lane's own runs
+// are the upper levels of that tree and the shuffles over the KS lanes the lower ones.  So R can follow the batch (few
+// sequences: fewer rows a lane and more lanes) without changing a bit of the result.
 template <int R>
-__global__ void __launch_bounds__(128) retention_walk_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
+__global__ void __launch_bounds__(256) retention_walk_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
                                                               const float* __restrict__ vn, const float* __restrict__ decay,
                                                               float* __restrict__ state, long long state_stride,
                                                               float* __restrict__ out, long long out_stride,
@@ -87,6 +91,7 @@ __global__ void __launch_bounds__(128) retention_walk_kernel(const float* __rest
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(16) float sm[];
+  constexpr int NJ = R / 4;  // runs of four rows a lane
   const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * CT;
   const int q_begin = qsl[b], q_len = qsl[b + 1] - q_begin;
   const int slot = state_slots[b];
@@ -109,7 +114,7 @@ __global__ void __launch_bounds__(128) retention_walk_kernel(const float* __rest
   // what no copy ever writes is zero for good: rows of q and k beyond dk, value columns beyond the tile's
   for (int idx = tid; idx < 2 * stage; idx += nthreads) buf[idx] = 0.f;
   __syncthreads();
-  // register i of lane s holds row ((i / 4) * KS + s) * 4 + i % 4
+  // register i of lane s holds row ((i / 4) * KS + s) * 4 + i % 4: run i / 4 of the lane is run (i / 4) * KS + s of the column
   float S[R];
 #pragma unroll
   for (int i = 0; i < R; ++i) S[i] = St[(((i >> 2) * KS + s) * 4 + (i & 3)) * lds + col];
@@ -146,25 +151,39 @@ __global__ void __launch_bounds__(128) retention_walk_kernel(const float* __rest
     const float* bk = bq + TC * dkp;
     const float* bv = bk + TC * dkp;
     const int t0 = c * TC, nt = min(TC, q_len - t0);
+    float* orow = out + (size_t)(q_begin + t0) * out_stride + (size_t)h * dv + c0 + col;
+    const float4* q = reinterpret_cast<const float4*>(bq) + s;
+    const float4* k = reinterpret_cast<const float4*>(bk) + s;
+    const float* v = bv + col;
+    const bool writes = s == 0 && col < ncol;
+#pragma unroll(R >= 32 ? 2 : 4)
     for (int t = 0; t < nt; ++t) {
-      const float4* q = reinterpret_cast<const float4*>(bq + t * dkp) + s;
-      const float4* k = reinterpret_cast<const float4*>(bk + t * dkp) + s;
-      const float vv = bv[t * CT + col];
-      float p = 0.f;
+      const float vv = *v;
+      float pg[NJ];
 #pragma unroll
-      for (int j = 0; j < R / 4; ++j) {
+      for (int j = 0; j < NJ; ++j) {
         const float4 k4 = k[j * KS], q4 = q[j * KS];
         S[4 * j] = fmaf(a, S[4 * j], __fmul_rn(k4.x, vv));
-        p = fmaf(S[4 * j], q4.x, p);
         S[4 * j + 1] = fmaf(a, S[4 * j + 1], __fmul_rn(k4.y, vv));
-        p = fmaf(S[4 * j + 1], q4.y, p);
         S[4 * j + 2] = fmaf(a, S[4 * j + 2], __fmul_rn(k4.z, vv));
-        p = fmaf(S[4 * j + 2], q4.z, p);
         S[4 * j + 3] = fmaf(a, S[4 * j + 3], __fmul_rn(k4.w, vv));
-        p = fmaf(S[4 * j + 3], q4.w, p);
+        pg[j] = fmaf(S[4 * j + 3], q4.w, fmaf(S[4 * j + 2], q4.z, fmaf(S[4 * j + 1], q4.y, __fmul_rn(S[4 * j], q4.x))));
       }
-      for (int o = KS >> 1; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-      if (s == 0 && col < ncol) out[(size_t)(q_begin + t0 + t) * out_stride + (size_t)h * dv + c0 + col] = p;
+#pragma unroll
+      for (int half = NJ / 2; half > 0; half >>= 1) {
+#pragma unroll
+        for (int j = 0; j < half; ++j) pg[j] = __fadd_rn(pg[j], pg[j + half]);
+      }
+      float p = pg[0];
+      // the lanes' parts, the halves of the row range first; levels a column has no lanes for are skipped (KS is one for the CTA)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        if (o < KS) p = __fadd_rn(p, __shfl_xor_sync(0xffffffffu, p, o));
+      if (writes) *orow = p;
+      q += dkp / 4;
+      k += dkp / 4;
+      v += CT;
+      orow += out_stride;
     }
     __syncthreads();  // the chunk is used up: the copy after next may overwrite it
   }
@@ -187,14 +206,14 @@ inline int pow2_at_least(int v) {
 template <int R>
 int launch_walk(const float* qn, const float* kn, const float* vn, const float* decay, float* state, long long state_stride, float* out,
                 long long out_stride, const int* qsl, const int* state_slots, int B, int H, int dk, int dv, cudaStream_t st) {
-  int KS = pow2_at_least((dk + R - 1) / R);
+  const int KS = pow2_at_least((dk + R - 1) / R);
   if (KS > 32) return (int)cudaErrorInvalidValue;
-  int CT = 128 / KS;
+  int CT = (R >= 32 ? 128 : 256) / KS;  // 32 rows a lane take 128 registers: smaller CTAs fit an SM better
   const int cols = pow2_at_least(dv);
   if (CT > cols) CT = cols;
   if (CT * KS < 32) CT = 32 / KS;
   // few (sequence, head) pairs: narrower tiles, so that there are CTAs for every SM
-  while (CT * KS > 32 && CT > 4 && (long long)B * H * ((dv + CT - 1) / CT) < 2 * 148) CT >>= 1;
+  while (CT * KS > 64 && CT > 4 && (long long)B * H * ((dv + CT - 1) / CT) < 148) CT >>= 1;
   const int dkp = KS * R;
   const size_t smem = (size_t)(((dkp * (CT + 1) + 3) & ~3) + 2 * TC * (2 * dkp + CT)) * sizeof(float);
   auto kern = retention_walk_kernel<R>;
@@ -204,6 +223,20 @@ int launch_walk(const float* qn, const float* kn, const float* vn, const float* 
   }
   return launch(kern, dim3((dv + CT - 1) / CT, H, B), dim3(KS * CT), smem, st, qn, kn, vn, decay, state, state_stride, out, out_stride,
                 qsl, state_slots, H, dk, dv, KS, CT);
+}
+
+// Rows a lane: as many (up to 32) as still leave a warp for every warp scheduler of the device; a state of few heads in a
+// step of few sequences is spread thin instead, since the walk over a sequence is a chain that only other lanes can hide
+// (one sequence of 2,048 tokens, 16 heads of 128 x 128: 536 us with 32 rows a lane, 460 us with 16 or 8, 480 us with 4;
+// eight sequences of 256 tokens: 219, 244, 247 and 336 us).
+inline int rows_per_lane(int B, int H, int dk, int dv) {
+  int best = 32;
+  for (int r = 32; r >= 4; r >>= 1) {
+    if ((dk + r - 1) / r > 32) break;  // more lanes a column than a warp has
+    best = r;
+    if ((long long)B * H * dv * pow2_at_least((dk + r - 1) / r) / 32 >= 4 * 148) break;
+  }
+  return best;
 }
 
 }  // namespace
@@ -226,13 +259,14 @@ int launch_walk(const float* qn, const float* kn, const float* vn, const float* 
                     x_stride, q_off, k_off, v_off, positions, inv_freq, rot, split_pairs, k_scale, N, H, dk, dv, qn,    \
                     kn, vn);                                                                                            \
     if (rc) return rc;                                                                                                  \
-    if (dk <= 16)                                                                                                       \
+    const int r = rows_per_lane(B, H, dk, dv);                                                                          \
+    if (r == 4)                                                                                                         \
       return launch_walk<4>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,    \
                             st);                                                                                        \
-    if (dk <= 32)                                                                                                       \
+    if (r == 8)                                                                                                         \
       return launch_walk<8>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,    \
                             st);                                                                                        \
-    if (dk <= 64)                                                                                                       \
+    if (r == 16)                                                                                                        \
       return launch_walk<16>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,   \
                              st);                                                                                       \
     return launch_walk<32>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,     \

@@ -46,7 +46,7 @@ def dense(ff):
     return {"kind": "dense", "ff": ff}
 
 
-def moe(experts, top, ff, limit=2.0):
+def moe(experts, top, ff, limit=2.5):
     return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
 
 
@@ -54,7 +54,7 @@ def layer(kind, mixer, mlp):
     return {"type": kind, "mixer": mixer, "mlp": mlp}
 
 
-def model(vocab, width, layers, eps=1e-6, scale=4.0, mult=0.7):
+def model(vocab, width, layers, eps=1e-6, scale=4.0, mult=0.75):
     return {"architecture": "Sonalix", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": scale}, "residual_mult": mult, "layers": layers}
 
 
@@ -76,7 +76,7 @@ CASES: dict[str, dict] = {
             layer("latent_attention", latent(2, 8, 16, 8, 40, 16, base=500.0), moe(4, 1, 20, limit=1.0)),
             layer("attention", attention(3, 3, 24, 8, window=37, softcap=5.0, base=300.0), moe(4, 1, 20, limit=1.0)),
             layer("attention", attention(3, 3, 24, 8, window=5, softcap=5.0, base=300.0, v_mix=False), dense(50)),
-            layer("retention", retention(3, 8, 8, [0.5, 0.96875, 1.0], rot=4), None),
+            layer("retention", retention(3, 8, 8, [0.5, 0.9375, 1.0], rot=4), None),
             layer("attention", attention(3, 3, 24, 8, window=37, softcap=5.0, base=300.0), moe(4, 1, 20, limit=1.0)),
             layer("latent_attention", latent(4, 16, 8, 16, 16, 24, rot=4), dense(64)),
         ], scale=1.0, mult=1.0),
@@ -96,10 +96,10 @@ CASES: dict[str, dict] = {
     # heads of 64 and 128, four heads a key head; a latent wider than a head; retention with keys of 128; many experts
     "d": {
         "config": model(211, 96, [
-            layer("attention", attention(8, 2, 64, 64, window=48, softcap=20.0), moe(16, 4, 64)),
+            layer("attention", attention(8, 2, 64, 64, window=48, softcap=25.0), moe(16, 4, 64)),
             layer("retention", retention(2, 128, 64, [0.984375, 0.998]), moe(16, 4, 64)),
             layer("latent_attention", latent(4, 32, 32, 48, 64, 96), moe(16, 4, 64)),
-            layer("attention", attention(8, 2, 64, 64, window=48, softcap=20.0), dense(160)),
+            layer("attention", attention(8, 2, 64, 64, window=48, softcap=25.0), dense(160)),
             layer("retention", retention(4, 64, 128, [0.9, 0.95, 0.99, 0.999], rot=32), None),
         ], eps=1e-5, scale=9.0, mult=0.5),
         "block_size": 16,
@@ -209,7 +209,7 @@ def random_config(seed: int) -> dict:
                               scale=rng.uniform(0.05, 0.3))  # fmt: skip
         elif kind == "retention":
             heads, dim = rng.choice([1, 2, 3, 6]), rng.choice([8, 16, 20, 48, 64, 96])
-            mixer = retention(heads, dim, rng.choice([8, 12, 32, 40, 100]), [rng.choice([0.5, 0.9, 0.96875, 0.99, 0.9995]) for _ in range(heads)],
+            mixer = retention(heads, dim, rng.choice([8, 12, 32, 40, 100]), [rng.choice([0.5, 0.9, 0.9375, 0.99, 0.9995]) for _ in range(heads)],
                               rot=rng.choice([0, dim, 2 * rng.randint(1, dim // 2)]), base=rng.choice([100.0, 1e6]))  # fmt: skip
         else:
             heads, dim, rot = rng.choice([1, 2, 5, 8, 12]), rng.choice([8, 16, 32]), rng.choice([8, 16, 32, 64])

@@ -417,7 +417,7 @@ def test_retention_through_the_state(dtype, heads, dk, dv, rot, t):
 
     rt = runtime(dtype)
     width, eps = 72, 1e-6
-    decay = [[0.9, 0.99, 0.96875, 1.0][h % 4] for h in range(heads)]
+    decay = [[0.9, 0.99, 0.9375, 1.0][h % 4] for h in range(heads)]
     m = retention(heads, dk, dv, decay, rot=rot, base=1000.0)
     pos = PartSpec("rotary", {"head_dim": dk, "rotary_dim": rot, "theta": 1000.0, "interleaved": False}) if rot else None
     part = build_part("mixer", PartSpec("retention", {"hidden_size": width, "num_heads": heads, "head_dim": dk, "v_head_dim": dv, "decay": decay, "eps": eps, "position": pos}), "m.")
@@ -503,7 +503,7 @@ def test_router_with_a_bias_alone(experts, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("ff,limit", [(40, 2.0), (20, 0.7)])
+@pytest.mark.parametrize("ff,limit", [(40, 2.5), (20, 0.7)])
 @pytest.mark.parametrize("n", [1, 7, 30, 150, 400])
 def test_gated_experts(dtype, n, ff, limit):
     """The feed-forward part against the plain one, for one token, a few and many (several tiles an expert; from 64 rows an
