@@ -24,7 +24,7 @@ using namespace kvf;
 
 namespace {
 
-constexpr int TC = 16;  // tokens per chunk of the walk
+constexpr int TC = 16;  // tokens per chunk of the walk, at most
 
 template <typename T>
 __global__ void __launch_bounds__(128) retention_prepare_kernel(const T* __restrict__ x, long long x_stride, int q_off, int k_off,
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256) retention_walk_kernel(const float* __rest
                                                               float* __restrict__ state, long long state_stride,
                                                               float* __restrict__ out, long long out_stride,
                                                               const int* __restrict__ qsl, const int* __restrict__ state_slots,
-                                                              int H, int dk, int dv, int KS, int CT) {
+                                                              int H, int dk, int dv, int KS, int CT, int tc) {
   pdl_launch();
   pdl_wait();
   extern __shared__ __align__(16) float sm[];
@@ -102,17 +102,30 @@ __global__ void __launch_bounds__(256) retention_walk_kernel(const float* __rest
   const int lds = CT + 1;
   float* St = sm;                       // [dkp][CT + 1]: the state tile on its way in and out
   const int st_floats = (dkp * lds + 3) & ~3;
-  const int stage = TC * (2 * dkp + CT);  // q [TC][dkp], k [TC][dkp], v [TC][CT]
+  // tc tokens a chunk (16, or as many as the step's longest sequence brings when that is fewer)
+  const int stage = tc * (2 * dkp + CT);  // q [tc][dkp], k [tc][dkp], v [tc][CT]
   float* buf = sm + st_floats;
   const float a = decay[h];
 
   float* sbase = state + (size_t)slot * state_stride + (size_t)h * dk * dv + c0;
-  for (int idx = tid; idx < dkp * CT; idx += nthreads) {
-    const int r = idx / CT, c = idx - r * CT;
-    St[r * lds + c] = (r < dk && c < ncol) ? sbase[(size_t)r * dv + c] : 0.f;
+  // whole tiles of whole rows go four numbers at a time
+  const bool tile4 = dkp == dk && ncol == CT && (CT & 3) == 0 && (dv & 3) == 0 && (((uintptr_t)sbase) & 15) == 0;
+  if (tile4) {
+    const int c4 = CT >> 2;
+    for (int idx = tid; idx < dk * c4; idx += nthreads) {
+      const int r = idx / c4, c = (idx - r * c4) << 2;
+      const float4 t4 = *reinterpret_cast<const float4*>(sbase + (size_t)r * dv + c);
+      float* d = St + r * lds + c;
+      d[0] = t4.x; d[1] = t4.y; d[2] = t4.z; d[3] = t4.w;
+    }
+  } else {
+    for (int idx = tid; idx < dkp * CT; idx += nthreads) {
+      const int r = idx / CT, c = idx - r * CT;
+      St[r * lds + c] = (r < dk && c < ncol) ? sbase[(size_t)r * dv + c] : 0.f;
+    }
+    // what no copy ever writes is zero for good: rows of q and k beyond dk, value columns beyond the tile's
+    for (int idx = tid; idx < 2 * stage; idx += nthreads) buf[idx] = 0.f;
   }
-  // what no copy ever writes is zero for good: rows of q and k beyond dk, value columns beyond the tile's
-  for (int idx = tid; idx < 2 * stage; idx += nthreads) buf[idx] = 0.f;
   __syncthreads();
   // register i of lane s holds row ((i / 4) * KS + s) * 4 + i % 4: run i / 4 of the lane is run (i / 4) * KS + s of the column
   float S[R];
@@ -122,9 +135,9 @@ __global__ void __launch_bounds__(256) retention_walk_kernel(const float* __rest
   const bool wide_qk = (dk & 3) == 0, wide_v = (dv & 3) == 0 && (c0 & 3) == 0 && (ncol & 3) == 0;
   auto issue = [&](int chunk) {
     float* bq = buf + (chunk & 1) * stage;
-    float* bk = bq + TC * dkp;
-    float* bv = bk + TC * dkp;
-    const int t0 = chunk * TC, nt = min(TC, q_len - t0);
+    float* bk = bq + tc * dkp;
+    float* bv = bk + tc * dkp;
+    const int t0 = chunk * tc, nt = min(tc, q_len - t0);
     const int per = wide_qk ? dk / 4 : dk;
     for (int idx = tid; idx < nt * per; idx += nthreads) {
       const int t = idx / per, j = (idx - t * per) * (wide_qk ? 4 : 1);
@@ -139,7 +152,7 @@ __global__ void __launch_bounds__(256) retention_walk_kernel(const float* __rest
     }
   };
 
-  const int nchunks = (q_len + TC - 1) / TC;
+  const int nchunks = (q_len + tc - 1) / tc;
   issue(0);
   asm volatile("cp.async.commit_group;\n" ::);
   for (int c = 0; c < nchunks; ++c) {
@@ -148,9 +161,9 @@ __global__ void __launch_bounds__(256) retention_walk_kernel(const float* __rest
     asm volatile("cp.async.wait_group 1;\n" ::);
     __syncthreads();
     const float* bq = buf + (c & 1) * stage;
-    const float* bk = bq + TC * dkp;
-    const float* bv = bk + TC * dkp;
-    const int t0 = c * TC, nt = min(TC, q_len - t0);
+    const float* bk = bq + tc * dkp;
+    const float* bv = bk + tc * dkp;
+    const int t0 = c * tc, nt = min(tc, q_len - t0);
     float* orow = out + (size_t)(q_begin + t0) * out_stride + (size_t)h * dv + c0 + col;
     const float4* q = reinterpret_cast<const float4*>(bq) + s;
     const float4* k = reinterpret_cast<const float4*>(bk) + s;
@@ -191,6 +204,15 @@ __global__ void __launch_bounds__(256) retention_walk_kernel(const float* __rest
 #pragma unroll
   for (int i = 0; i < R; ++i) St[(((i >> 2) * KS + s) * 4 + (i & 3)) * lds + col] = S[i];
   __syncthreads();
+  if (tile4) {
+    const int c4 = CT >> 2;
+    for (int idx = tid; idx < dk * c4; idx += nthreads) {
+      const int r = idx / c4, c = (idx - r * c4) << 2;
+      const float* d = St + r * lds + c;
+      *reinterpret_cast<float4*>(sbase + (size_t)r * dv + c) = make_float4(d[0], d[1], d[2], d[3]);
+    }
+    return;
+  }
   for (int idx = tid; idx < dk * ncol; idx += nthreads) {
     const int r = idx / ncol, c = idx - r * ncol;
     sbase[(size_t)r * dv + c] = St[r * lds + c];
@@ -205,7 +227,7 @@ inline int pow2_at_least(int v) {
 
 template <int R>
 int launch_walk(const float* qn, const float* kn, const float* vn, const float* decay, float* state, long long state_stride, float* out,
-                long long out_stride, const int* qsl, const int* state_slots, int B, int H, int dk, int dv, cudaStream_t st) {
+                long long out_stride, const int* qsl, const int* state_slots, int B, int H, int dk, int dv, int tc, cudaStream_t st) {
   const int KS = pow2_at_least((dk + R - 1) / R);
   if (KS > 32) return (int)cudaErrorInvalidValue;
   int CT = (R >= 32 ? 128 : 256) / KS;  // 32 rows a lane take 128 registers: smaller CTAs fit an SM better
@@ -215,14 +237,14 @@ int launch_walk(const float* qn, const float* kn, const float* vn, const float* 
   // few (sequence, head) pairs: narrower tiles, so that there are CTAs for every SM
   while (CT * KS > 64 && CT > 4 && (long long)B * H * ((dv + CT - 1) / CT) < 148) CT >>= 1;
   const int dkp = KS * R;
-  const size_t smem = (size_t)(((dkp * (CT + 1) + 3) & ~3) + 2 * TC * (2 * dkp + CT)) * sizeof(float);
+  const size_t smem = (size_t)(((dkp * (CT + 1) + 3) & ~3) + 2 * tc * (2 * dkp + CT)) * sizeof(float);
   auto kern = retention_walk_kernel<R>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   return launch(kern, dim3((dv + CT - 1) / CT, H, B), dim3(KS * CT), smem, st, qn, kn, vn, decay, state, state_stride, out, out_stride,
-                qsl, state_slots, H, dk, dv, KS, CT);
+                qsl, state_slots, H, dk, dv, KS, CT, tc);
 }
 
 // Rows a lane: as many (up to 32) as still leave a warp for every warp scheduler of the device; a state of few heads in a
@@ -243,13 +265,15 @@ inline int rows_per_lane(int B, int H, int dk, int dv) {
 
 // x: rows of the projections (q heads from q_off, k heads from k_off, v heads from v_off; H heads each of dk, dk, dv).
 // qn, kn [N][H*dk] and vn [N][H*dv]: float scratch.  state: float, slot i at state + i * state_stride, [H][dk][dv].
-// out: float [N][H*dv] (row stride out_stride).  decay: float [H].  Two launches.
+// out: float [N][H*dv] (row stride out_stride).  decay: float [H].  max_q_len: the most rows a sequence of the step brings
+// (0: unknown); a step of single tokens stages one token, not sixteen.  Two launches.
 #define KVF_RETENTION_API(SUF, T)                                                                                       \
   KVF_API int kvf_retention_##SUF(const void* x, long long x_stride, int q_off, int k_off, int v_off,                   \
                                   const int* positions, const float* inv_freq, int rot, int split_pairs,                \
                                   float k_scale, const float* decay, float* state, long long state_stride, float* out,  \
                                   long long out_stride, const int* qsl, const int* state_slots, int B, long long N,     \
-                                  int H, int dk, int dv, float* qn, float* kn, float* vn, cudaStream_t st) {            \
+                                  int H, int dk, int dv, float* qn, float* kn, float* vn, int max_q_len,                \
+                                  cudaStream_t st) {                                                                    \
     if (B <= 0 || N <= 0) return 0;                                                                                     \
     if (H <= 0 || dk <= 0 || dk > 512 || dv <= 0 || rot < 0 || rot > dk || (rot & 1) || (unsigned)B > 65535u ||         \
         (unsigned)H > 65535u)                                                                                           \
@@ -260,17 +284,18 @@ inline int rows_per_lane(int B, int H, int dk, int dv) {
                     kn, vn);                                                                                            \
     if (rc) return rc;                                                                                                  \
     const int r = rows_per_lane(B, H, dk, dv);                                                                          \
+    const int tc = max_q_len > 0 && max_q_len < TC ? max_q_len : TC;                                                    \
     if (r == 4)                                                                                                         \
       return launch_walk<4>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,    \
-                            st);                                                                                        \
+                            tc, st);                                                                                        \
     if (r == 8)                                                                                                         \
       return launch_walk<8>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,    \
-                            st);                                                                                        \
+                            tc, st);                                                                                        \
     if (r == 16)                                                                                                        \
       return launch_walk<16>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,   \
-                             st);                                                                                       \
+                             tc, st);                                                                                       \
     return launch_walk<32>(qn, kn, vn, decay, state, state_stride, out, out_stride, qsl, state_slots, B, H, dk, dv,     \
-                           st);                                                                                         \
+                           tc, st);                                                                                         \
   }
 
 KVF_RETENTION_API(f32, float)

@@ -72,7 +72,7 @@ _SIGNATURES = {
     "kvf_talking_mma_ok": "iiiiii",
     "kvf_gated_set_pdl": "i",
     # library "decay"
-    "kvf_retention_{s}": "pliiippiifpplplppiliiipppp",
+    "kvf_retention_{s}": "pliiippiifpplplppiliiipppip",
     "kvf_tanh_norm_{s}": "pppilfppppplip",
     "kvf_decay_set_pdl": "i",
 }
@@ -1990,13 +1990,15 @@ def retention(
     x: torch.Tensor, q_off: int, k_off: int, v_off: int, positions: torch.Tensor, inv_freq: torch.Tensor | None, interleaved: bool,
     k_scale: float, decay: torch.Tensor, state: torch.Tensor, out: torch.Tensor, qsl: torch.Tensor, state_slots: torch.Tensor,
     num_seqs: int, num_heads: int, dk: int, dv: int, scratch: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+    max_query_len: int = 0,
 ) -> None:  # fmt: skip
     """Retention over a flat batch, token by token per sequence, on the float state ``S [heads, dk, dv]`` of each
     sequence's slot: ``S <- decay[h] S + k v^T``, ``out = S^T q`` (float ``[N, H*dv]``).  Rows of ``x`` hold the
     projections: ``H`` query heads of ``dk`` from column ``q_off``, key heads from ``k_off``, value heads of ``dv`` from
     ``v_off``.  The first ``2*len(inv_freq)`` dims of q and k turn with the position (split pairs ``(i, i + rot/2)``
     unless ``interleaved``), then k is multiplied by ``k_scale``; all of that in float.  ``scratch``: float buffers
-    ``(qn [N, H*dk], kn [N, H*dk], vn [N, H*dv])``; without it they are allocated here.  Two launches."""
+    ``(qn [N, H*dk], kn [N, H*dk], vn [N, H*dv])``; without it they are allocated here.  ``max_query_len`` (0 = unknown):
+    the most rows a sequence of the step brings (a step of single tokens stages less).  Two launches."""
     s = _suffix(x.dtype)
     _rows2d(x, None, "x")
     n = x.shape[0]
@@ -2034,7 +2036,7 @@ def retention(
         _fn(name, DECAY_LIB)(
             _ptr(x), x.stride(0), int(q_off), int(k_off), int(v_off), _ptr(positions), _ptr(inv_freq) if rot else None, rot,
             0 if interleaved else 1, float(k_scale), _ptr(decay), sptr, sstride, _ptr(out), out.stride(0), _ptr(qsl), _ptr(state_slots),
-            int(num_seqs), n, h, int(dk), int(dv), _ptr(qn), _ptr(kn), _ptr(vn), _stream(),
+            int(num_seqs), n, h, int(dk), int(dv), _ptr(qn), _ptr(kn), _ptr(vn), int(max_query_len), _stream(),
         ),
         name,
         2,

@@ -100,7 +100,7 @@ class Retention(Mixer):
         )
         ops.retention(
             y, 0, self.k_off, self.v_off, ctx.positions, self.inv_freq, self.interleaved, self.key_scale, self.decay, cache.state, o,
-            ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, h, dk, dv, scratch,
+            ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, h, dk, dv, scratch, max_query_len=ctx.max_query_len,
         )  # fmt: skip
         out = rt.buf("retention.out", n, h * dv)
         gate = y[:, self.g_off : self.g_off + h * dv] if self.gate else None
