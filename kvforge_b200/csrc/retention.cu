@@ -14,6 +14,7 @@
 //             lane makes  S <- a S + k v  and its part of  S^T q  in one pass; the parts are added in a tree whose
 //             shape follows dk alone.  Chunks of TC tokens come in through a cp.async double buffer; the state tile passes through
 //             shared memory so that global memory sees whole rows.
+//   gate    : every head's read-out divided by its root mean square and multiplied by act(gate).
 //
 // The state after a token is the same bits however the sequence was cut into steps (the walk is token by token,
 // and every sum has an order fixed by dk alone, however many rows a lane holds), so a token's output does not
@@ -219,6 +220,36 @@ __global__ void __launch_bounds__(256) retention_walk_kernel(const float* __rest
   }
 }
 
+// What follows the walk: every head's read-out divided by its root mean square (no weight) and multiplied by
+// act(gate), a warp per (token, head).  act: 0 none, 1 silu, 2 the logistic function; float arithmetic, one rounding.
+template <typename T>
+__global__ void __launch_bounds__(128) retention_gate_kernel(const float* __restrict__ o, long long o_stride, const T* __restrict__ gate,
+                                                              long long gate_stride, float eps, int act, long long pairs, int H, int dv,
+                                                              T* __restrict__ out, long long out_stride) {
+  pdl_launch();
+  pdl_wait();
+  const long long pair = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const int lane = threadIdx.x & 31;
+  const long long n = pair / H;
+  const int h = (int)(pair - n * H);
+  const float* row = o + (size_t)n * o_stride + (size_t)h * dv;
+  float ss = 0.f;
+  for (int j = lane; j < dv; j += 32) ss = fmaf(row[j], row[j], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)dv + eps);
+  const T* g = gate ? gate + (size_t)n * gate_stride + (size_t)h * dv : nullptr;
+  T* dst = out + (size_t)n * out_stride + (size_t)h * dv;
+  for (int j = lane; j < dv; j += 32) {
+    float y = row[j] * inv;
+    if (act) {
+      const float z = to_float<T>(g[j]), sg = 1.f / (1.f + expf(-z));
+      y *= act == 1 ? z * sg : sg;
+    }
+    dst[j] = from_float<T>(y);
+  }
+}
+
 inline int pow2_at_least(int v) {
   int p = 1;
   while (p < v) p <<= 1;
@@ -298,5 +329,18 @@ inline int rows_per_lane(int B, int H, int dk, int dv) {
                            tc, st);                                                                                         \
   }
 
+#define KVF_RETENTION_GATE_API(SUF, T)                                                                                  \
+  KVF_API int kvf_retention_gate_##SUF(const float* o, long long o_stride, const void* gate, long long gate_stride,     \
+                                       float eps, int act, long long N, int H, int dv, void* out, long long out_stride, \
+                                       cudaStream_t st) {                                                               \
+    const long long pairs = N * H;                                                                                      \
+    if (pairs <= 0) return 0;                                                                                           \
+    if ((act && !gate) || act < 0 || act > 2 || dv <= 0) return (int)cudaErrorInvalidValue;                             \
+    return launch(retention_gate_kernel<T>, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, st, o, o_stride,           \
+                  (const T*)gate, gate_stride, eps, act, pairs, H, dv, (T*)out, out_stride);                            \
+  }
+
+KVF_RETENTION_GATE_API(f32, float)
+KVF_RETENTION_GATE_API(bf16, bf16)
 KVF_RETENTION_API(f32, float)
 KVF_RETENTION_API(bf16, bf16)

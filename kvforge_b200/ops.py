@@ -73,6 +73,7 @@ _SIGNATURES = {
     "kvf_gated_set_pdl": "i",
     # library "decay"
     "kvf_retention_{s}": "pliiippiifpplplppiliiipppip",
+    "kvf_retention_gate_{s}": "plplfiliiplp",
     "kvf_tanh_norm_{s}": "pppilfppppplip",
     "kvf_decay_set_pdl": "i",
 }
@@ -2041,3 +2042,26 @@ def retention(
         name,
         2,
     )  # fmt: skip
+
+
+def retention_gate(o: torch.Tensor, gate: torch.Tensor | None, eps: float, out: torch.Tensor, num_heads: int, dv: int, activation: str | None = "silu") -> None:
+    """``out[n, h, :] = o / sqrt(mean(o^2) + eps) * act(gate)`` per token and head (a unit norm without a weight); ``o``
+    float ``[N, H*dv]``, ``gate`` and ``out`` in the storage type (column ranges of wider rows are fine), ``activation``:
+    ``"silu"``, ``"sigmoid"`` or ``None`` (no gate)."""
+    s = _suffix(out.dtype)
+    _rows2d(o, torch.float32, "o")
+    _rows2d(out, None, "out")
+    n = o.shape[0]
+    if o.shape[1] != num_heads * dv or tuple(out.shape) != (n, num_heads * dv):
+        raise ValueError("retention_gate: shapes do not agree")
+    act = {None: 0, "silu": 1, "sigmoid": 2}.get(activation, -1)
+    if act < 0:
+        raise ValueError("retention_gate: activation must be 'silu', 'sigmoid' or None")
+    gptr, gstride = None, 0
+    if act:
+        _rows2d(gate, out.dtype, "gate")
+        if tuple(gate.shape) != (n, num_heads * dv):
+            raise ValueError("retention_gate: gate shape")
+        gptr, gstride = _ptr(gate), gate.stride(0)
+    name = f"kvf_retention_gate_{s}"
+    _check(_fn(name, DECAY_LIB)(_ptr(o), o.stride(0), gptr, gstride, float(eps), act, n, num_heads, dv, _ptr(out), out.stride(0), _stream()), name)

@@ -74,7 +74,6 @@ class Retention(Mixer):
         self.w_in = torch.cat(mats, dim=0).contiguous()
         self.w_o = weights["o"].contiguous()
         self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=rt.device)
-        self.ones = torch.ones(self.dv, dtype=torch.float32, device=rt.device)  # the heads' norm has no weight
         if self.position_spec is not None and self.position is None:
             self.position = build_part("position", self.position_spec)
             self.position.bind({}, rt)
@@ -104,5 +103,5 @@ class Retention(Mixer):
         )  # fmt: skip
         out = rt.buf("retention.out", n, h * dv)
         gate = y[:, self.g_off : self.g_off + h * dv] if self.gate else None
-        ops.gated_head_norm(o, gate, self.ones, self.eps, out, h, dv, self.gate)
+        ops.retention_gate(o, gate, self.eps, out, h, dv, self.gate)
         return project(rt, "retention.proj", out, self.w_o, ctx)
