@@ -34,8 +34,8 @@ class Retention(Mixer):
         self.decay_values = [float(a) for a in p["decay"]]
         if len(self.decay_values) != self.nh:
             raise ValueError("retention needs one decay per head")
-        if not 0 < self.dk <= ops.RETENTION_MAX_KEY_DIM or self.dv <= 0 or self.dk % 2:
-            raise ValueError(f"retention takes even key heads of at most {ops.RETENTION_MAX_KEY_DIM} numbers")
+        if not 0 < self.dk <= ops.RETENTION_MAX_KEY_DIM or self.dv <= 0:
+            raise ValueError(f"retention takes key heads of at most {ops.RETENTION_MAX_KEY_DIM} numbers")
         self.eps = float(p["eps"])
         self.key_scale = float(p.get("key_scale") or self.dk**-0.5)
         self.gate = p.get("gate", "silu")

@@ -410,7 +410,7 @@ def test_one_far_key_and_the_sink_share_the_weight():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dk,dv,rot,t", [(2, 16, 24, 16, 45), (3, 8, 8, 4, 60), (1, 32, 12, 0, 50), (2, 128, 64, 128, 150), (4, 64, 128, 32, 90), (2, 20, 100, 6, 40), (1, 256, 40, 256, 70)])
+@pytest.mark.parametrize("heads,dk,dv,rot,t", [(2, 16, 24, 16, 45), (3, 8, 8, 4, 60), (1, 32, 12, 0, 50), (2, 128, 64, 128, 150), (4, 64, 128, 32, 90), (2, 20, 100, 6, 40), (1, 256, 40, 256, 70), (2, 9, 5, 4, 40), (1, 512, 8, 0, 40)])
 def test_retention_through_the_state(dtype, heads, dk, dv, rot, t):
     """Whole, in portions and token by token; in a slot that another request has used; beside another request."""
     from kvforge_b200.parts.base import LayerCache, PartSpec, build_part
