@@ -87,7 +87,12 @@ class EngineCore:
 
         self.block_size = cache.block_size
         per_block = bytes_per_block(self.model, cache.block_size, self.dtype)
-        self.num_blocks = cache.resolve_num_blocks(per_block)
+        if per_block == 0 and cache.num_blocks is None:
+            # no mixer keeps pages (state slots only): a memory budget says nothing, so the pool is as many
+            # (empty) pages as the requests that can be live could ever be asked to hold
+            self.num_blocks = max(1, max_num_seqs * -(-self.max_model_len // cache.block_size))
+        else:
+            self.num_blocks = cache.resolve_num_blocks(per_block)
         groups = [GroupSpec(g.need.kind, g.need.window, g.need.keep_first if g.need.kind == "window" else 0) for g in self.model.groups] or [GroupSpec()]
         self.block_manager = BlockManager(self.num_blocks, cache.block_size, cache.watermark, groups)
         self.state_slots = StateSlotPool(max_num_seqs)

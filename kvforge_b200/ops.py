@@ -561,10 +561,11 @@ def paged_attention(
     ``dv``: size of a value head when it differs from ``d`` (``vcache`` is then
     ``[num_blocks, nkv, block_size, dv]`` and ``out`` ``[N, nh*dv]``); only the FP32-pipe kernel
     takes such a shape.  So it is with ``vcache is kcache`` (a value is the first ``dv`` numbers of
-    its key), with ``keep_first`` (under a window, the first keys of every sequence stay visible at
-    any distance), with ``bias`` (added to the scaled scores, by distance and head), with ``softcap``
-    (``c > 0``: a scaled score ``s`` becomes ``c * tanh(s / c)``) and with ``sinks`` (float ``[nh]``: ``exp(sinks[h])``
-    joins the softmax's denominator of head ``h``; it has no key and no value).
+    its key).  ``keep_first`` (under a window, the first keys of every sequence stay visible at any
+    distance), ``bias`` (added to the scaled scores, by distance and head), ``softcap`` (``c > 0``: a scaled
+    score ``s`` becomes ``c * tanh(s / c)``) and ``sinks`` (float ``[nh]``: ``exp(sinks[h])`` joins the softmax's
+    denominator of head ``h``; it has no key and no value) are taken by the FP32-pipe kernel and, for bfloat16
+    heads of 64 or 128 with values as wide, by the mma.sync kernels.
 
     ``q``: rows of ``q_stride`` elements whose first ``nh*d`` are the query heads; ``out``:
     ``[N, nh*d]``.  With ``scratch`` (and every sequence holding one query) the decode form

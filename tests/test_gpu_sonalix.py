@@ -203,6 +203,33 @@ def test_the_trace_program_reads_a_folder_and_writes_logits(models, tmp_path):
     check(steps, outs, ref, scale, TOL["float32"])
 
 
+@pytest.mark.parametrize("kind", ["retention", "attention", "latent_attention"])
+def test_models_of_one_kind_of_mixer(tmp_path, kind):
+    """A model may have layers of one kind only: retention alone keeps no pages at all (state slots only), attention
+    alone no state."""
+    from sonalix_cases import dense, layer, model, moe
+
+    mixer = {"retention": retention(2, 24, 16, [0.9, 0.97], rot=12), "attention": attention(4, 2, 16, 8, window=9, softcap=12.0),
+             "latent_attention": latent(2, 16, 8, 16, 24, 32)}[kind]  # fmt: skip
+    config = model(77, 56, [layer(kind, mixer, dense(40)), layer(kind, mixer, moe(5, 2, 24))], mult=0.9)
+    for dtype, fixed in (("float32", False), ("bfloat16", True)):
+        folder, reqs, ref, scale, w = build(tmp_path, f"{kind}-{dtype}", config, random_tensors(config, 7, fixed_choice=fixed), [60, 2, 31, 85], seed=3)
+        for regime in ("whole", "portions", "mixed"):
+            steps = regime_steps(reqs, regime)
+            outs, _ = run_trace(folder, dtype, steps, 8)
+            check(steps, outs, ref, scale, TOL[dtype])
+    if kind == "retention":
+        from kvforge_b200 import EngineConfig, InferenceEngine, SamplingParams, SchedulerConfig
+
+        engine = InferenceEngine(EngineConfig(scheduler=SchedulerConfig(max_num_seqs=2, max_num_batched_tokens=16, max_model_len=64), dtype="float32"), model=folder)
+        prompts = [tokens(77, n, 9 + n) for n in (5, 20, 1)]
+        outs = engine.generate(prompts, SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
+        wd = {k: v.double() for k, v in w.items()}
+        # the folder of the last storage type holds the weights whose router biases decide the choice
+        for p, o in zip(prompts, outs):
+            assert o.output_token_ids == plain.greedy(config, wd, p, 6)
+
+
 # ------------------------------------------------------------------ generation through the entry point
 
 
